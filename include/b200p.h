@@ -256,6 +256,88 @@ int b200p_peer_allgather(const void* const* peer_src, void* const* peer_flags, i
 /* host_out[0] = 1 if a handshake of this rank ever timed out (a peer stopped), else 0; synchronises `stream` */
 int b200p_peer_status(const void* flags_local, uint32_t* host_out, void* stream);
 
+/* ---- dense linear layers, ragged batches, gated delta rule, windowed latent attention ------------------------------------
+ * Nothing in the reference corresponds to these (its graphs are Llama-like): they carry decoder designs whose layers mix a
+ * recurrent state with a sliding-window attention over a shared low-rank latent.
+ *
+ * Ragged batch convention: a step brings nb "entries"; entry e owns the packed tokens [cu[e], cu[e+1]) and continues the
+ * sequence held in cache row rows[e], whose next position is lengths[rows[e]].  b200p_ragged_plan expands that to
+ * per-token arrays; every state-carrying kernel treats position 0 as "no history" (zero state, zero convolution inputs,
+ * the first-token bucket), so giving a row back is lengths[row] = 0 and nothing else. */
+
+/* b200p_gemm epilogues */
+enum {
+  B200P_GEMM_STORE = 0,      /* y[M,N] (dtype) = acc                                                             */
+  B200P_GEMM_STORE_F32 = 1,  /* y[M,N] (float) = acc                                                             */
+  B200P_GEMM_GLU_CLAMP = 2   /* rows 2i / 2i+1 of w are gate_i / up_i: y[M,N/2] (dtype) = g * sigmoid(1.702 g) * (u + 1),
+                                g = min(gate, limit), u = clamp(up, -limit, limit)                                  */
+};
+/* y = x . w^T, x [M,K] and w [N,K] in `dtype` (row strides ldx / ldw elements), fp32 accumulation; `batch` independent
+ * products at element strides stride_x / stride_w / stride_y.  B200P_F32 runs true fp32 FMAs in ascending k.  16-bit calls
+ * with K % 8 == 0 and 16-byte aligned rows take the tensor-core tile kernel (more than 8 rows) or the row-streaming kernel;
+ * everything else takes a generic kernel. */
+int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
+               int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype, int epilogue, float limit,
+               void* stream);
+
+/* t_row[t] = rows[e], t_pos[t] = lengths[rows[e]] + (t - cu[e]), t_off[t] = t - cu[e] for the entry e that owns token t */
+int b200p_ragged_plan(const int32_t* cu, const int32_t* rows, const int32_t* lengths, int32_t* t_row, int32_t* t_pos,
+                      int32_t* t_off, int nb, int64_t M, void* stream);
+/* end of a step: lengths[rows[e]] += cu[e+1] - cu[e]; last_token[rows[e]] = ids[cu[e+1] - 1] (entries with no token: nothing) */
+int b200p_ragged_advance(int32_t* lengths, int32_t* last_token, const int32_t* ids, const int32_t* cu, const int32_t* rows,
+                         int nb, void* stream);
+/* h[t,:] (float) = embed[ids[t],:] * scale + bigram[bucket(t),:]; bucket = (prev * mul_prev + ids[t] * mul_cur) mod buckets with
+ * prev the token before t in its sequence (ids[t-1] inside a portion, last_token[row] at its start), and row `buckets` of the
+ * table at position 0.  bigram may be NULL.  Tables [*, W] in `dtype`. */
+int b200p_embed_hashed(const int32_t* ids, const int32_t* t_row, const int32_t* t_pos, const int32_t* t_off,
+                       const int32_t* last_token, const void* embed, const void* bigram, float* h, int64_t M, int64_t W,
+                       int64_t V, float scale, int64_t buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
+/* Residual stream with a norm on both sides of a sublayer, one pass per row:
+ *   y given:      h += y / sqrt(mean(y^2) + eps) * w_post          (all fp32)
+ *   raw_out given: raw_out = h in `dtype`
+ *   x_out given:  x_out = h / sqrt(mean(h^2) + eps) * w_next in `dtype`
+ * rows [M, W]; weights fp32. */
+int b200p_norm_add_norm(const float* y, const float* w_post, float* h, const float* w_next, void* x_out, void* raw_out,
+                        int64_t M, int64_t W, float eps, int dtype, void* stream);
+/* out[t, c] (dtype) = gelu_tanh(gate[t, c]) * table[ids[t], col0 + c], c < d; gate fp32 [M, d], table [*, ld_table] `dtype` */
+int b200p_token_gate(const float* gate, const void* table, const int32_t* ids, void* out, int64_t M, int d, int64_t ld_table,
+                     int64_t col0, int dtype, void* stream);
+
+/* Gated delta rule, step 1.  proj fp32 [M, ldp] holds the fused projection [q | k | v | gate | b | a]: q, k (KH heads x dk) and
+ * v (H heads x dv) are columns [0, C), C = 2 KH dk + H dv.  Per channel a causal convolution of `taps` taps (conv_w [C, taps],
+ * last column = current token; inputs before position 0 are zero, inputs before the portion come from conv_state
+ * [rows, taps-1, C]) then silu; q and k are made unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q times dk^-1/2;
+ * beta = sigmoid(b); decay = exp(-exp(A_log) * softplus(a + dt_bias)).  Outputs fp32: qn, kn [M, KH dk], v [M, H dv],
+ * beta, decay [M, H]. */
+int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* conv_w, const float* conv_state,
+                     const float* A_log, const float* dt_bias, const int32_t* t_row, const int32_t* t_pos, const int32_t* t_off,
+                     float* qn, float* kn, float* v, float* beta, float* decay, int64_t M, int H, int KH, int dk, int dv,
+                     int taps, void* stream);
+/* step 2 (after b200p_delta_prep of the same step): conv_state of every entry's row takes the last taps-1 inputs */
+int b200p_delta_conv_commit(const float* proj, int64_t ldp, float* conv_state, const int32_t* cu, const int32_t* rows, int nb,
+                            int64_t C, int taps, void* stream);
+/* step 3: per entry and head, token by token in fp32: S *= decay; u = beta (v - S^T k); S += k u^T; o = S^T q.
+ * state [rows, H, dk, dv] fp32 is read (zero when the entry starts at position 0) and written back; head h reads q/k head
+ * h / (H / KH).  o fp32 [M, H dv]. */
+int b200p_delta_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay, float* state,
+                     const int32_t* cu, const int32_t* rows, const int32_t* lengths, float* o, int nb, int H, int KH, int dk,
+                     int dv, void* stream);
+/* step 4: out[t, h, :] (dtype) = o / sqrt(mean_dv(o^2) + eps) * norm_w * silu(gate[t, h, :]); gate = proj columns col_g.. */
+int b200p_delta_out(const float* o, const float* proj, int64_t ldp, int64_t col_g, const float* norm_w, void* out, int64_t M,
+                    int H, int dv, float eps, int dtype, void* stream);
+
+/* Latent attention, step 1.  proj fp32 [M, ldp] = [down-projected query (q_rank) | down-projected key/value (kv_rank)].
+ * cq_out [M, q_rank] (dtype) = rms_norm(query part) * wq; the key/value part, rms_norm * wkv, is written to
+ * cache[t_row, t_pos, :] (cache [rows, Tcap, kv_rank] in `dtype`).  kv_rank == 0: a layer that reads another layer's cache. */
+int b200p_latent_prep(const float* proj, int64_t ldp, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps,
+                      void* cq_out, void* cache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, int64_t M, int dtype,
+                      void* stream);
+/* step 2: H heads attend over the ONE latent per position (keys and values both): q fp32 [M, H, R] are the queries already
+ * carried into the latent space; token t at position p sees positions j with 0 <= p - j < window (window <= 0: all j <= p);
+ * fp32 softmax of q . c_j * scale; out [M, H, R] (dtype) = sum_j p_j c_j.  R <= 512. */
+int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, void* out,
+                      int64_t M, int H, int R, int64_t window, float scale, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,13 +63,47 @@ SIGNATURES = {
     "b200p_allreduce_rows_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _i32, _vp]),
     "b200p_peer_allgather": (_i32, [_vp, _vp, _i32, _i32, _vp, _i64, _vp]),
     "b200p_peer_status": (_i32, [_vp, _vp, _vp]),
+    # dense linear layers, ragged batches, gated delta rule, latent attention
+    "b200p_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
+    "b200p_ragged_plan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp]),
+    "b200p_ragged_advance": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _vp]),
+    "b200p_embed_hashed": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i64, _i64, _i64, _i32, _vp]),
+    "b200p_norm_add_norm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
+    "b200p_token_gate": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _vp]),
+    "b200p_delta_prep": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200p_delta_conv_commit": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp]),
+    "b200p_delta_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200p_delta_out": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _f32, _i32, _vp]),
+    "b200p_latent_prep": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp]),
+    "b200p_latent_attn": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _f32, _i32, _vp]),
 }
+
+# Translation units a model family needs (csrc/*.cu): the library can be linked from a subset, so that a fresh checkout
+# that serves one design compiles that design's kernels only.  ``None`` = every unit (libb200parallm.so).
+UNIT_SETS = {
+    "sequence": ("runtime", "dense_gemm", "ragged", "delta_rule", "latent_attn", "sampler"),
+}
+GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP = 0, 1, 2
 
 _lib = None
 
 
 class B200PError(RuntimeError):
     pass
+
+
+def _bind(path: str, partial: bool) -> C.CDLL:
+    L = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(L, name)          # AttributeError on the full library = header/library drift
+        except AttributeError:
+            if not partial:
+                raise
+            continue
+        fn.restype, fn.argtypes = res, args
+    return L
 
 
 def lib() -> C.CDLL:
@@ -80,11 +114,31 @@ def lib() -> C.CDLL:
             raise B200PError(
                 f"{LIB_PATH} not found: the CUDA extension is not built and there is no CPU fallback "
                 "(run `make -C mlx_parallm_b200/csrc`)")
-        L = C.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
-            fn = getattr(L, name)          # AttributeError here = header/library drift
-            fn.restype, fn.argtypes = res, args
-        _lib = L
+        _lib = _bind(LIB_PATH, partial=False)
+    return _lib
+
+
+def ensure_built(unit_set: str, verbose: bool = False) -> C.CDLL:
+    """Make sure a library that holds the kernels of ``unit_set`` (a key of UNIT_SETS) is loaded.  The complete library is
+    used when it exists; otherwise the set's translation units are compiled with nvcc for sm_100a and linked into
+    ``libb200parallm_<unit_set>.so`` next to it (first call only: make sees the objects afterwards).  A function of a unit
+    that is not in the set is absent from that library and raises AttributeError when called."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if os.path.exists(LIB_PATH):
+        return lib()
+    import subprocess
+    units = UNIT_SETS[unit_set]
+    part = os.path.join(_HERE, f"libb200parallm_{unit_set}.so")
+    cmd = ["make", "-C", os.path.join(_HERE, "csrc"), f"-j{min(8, os.cpu_count() or 1)}",
+           "SRCS=" + " ".join(u + ".cu" for u in units), "LIB=" + part]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0 or not os.path.exists(part):
+        raise B200PError(f"building {part} failed:\n{r.stdout[-4000:]}")
+    if verbose:
+        print(r.stdout)
+    _lib = _bind(part, partial=True)
     return _lib
 
 

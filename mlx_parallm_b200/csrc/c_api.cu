@@ -1,24 +1,9 @@
-// C-ABI glue: error plumbing, device checks and the path dispatchers of b200p_qmm / b200p_attn.
-#include <stdarg.h>
+// C-ABI glue: the path dispatchers of b200p_qmm / b200p_attn (error plumbing and device checks: runtime.cu).
 #include <stdlib.h>
 
 #include "common.cuh"
 
 namespace b200p {
-
-static thread_local char g_err[512] = "";
-
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-}
-
-int cuda_fail(cudaError_t e, const char* what) {
-  set_error("%s: %s", what, cudaGetErrorString(e));
-  return B200P_ERR_CUDA;
-}
 
 // implemented in the kernel translation units
 int qmv_launch(const void* x, const uint32_t* w, const void* s, const void* b, void* y, int64_t M, int64_t N,
@@ -67,61 +52,9 @@ static int g_mma_max_m = [] { const char* e = getenv("B200P_MMA_MAX_M"); return 
 static int g_gemv_max_m = [] { const char* e = getenv("B200P_GEMV_MAX_M"); return e ? atoi(e) : 4; }();
 static long long g_gemv_max_weights = [] { const char* e = getenv("B200P_GEMV_MAX_WEIGHTS"); return e ? atoll(e) : (1ll << 25); }();
 static int g_attn_path = 0;  // 0 auto, 1 generic, 2 tensor
-// 0 off, 1 every kernel, 2 only the tensor-path GEMM (B200P_PDL overrides the default at load time)
-static int g_pdl = [] { const char* e = getenv("B200P_PDL"); return e ? atoi(e) : 2; }();
-static int g_sm_count = -1;
-static int g_cc_major = -1;
-
-static int query_device() {
-  if (g_cc_major >= 0) return B200P_OK;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  cudaDeviceProp p;
-  e = cudaGetDeviceProperties(&p, dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
-  g_cc_major = p.major;
-  g_sm_count = p.multiProcessorCount;
-  return B200P_OK;
-}
-
-// per-class PDL mask for the non-GEMM kernels (see common.cuh); B200P_PDL=1 means every class
-static int g_pdl_mask = [] { const char* e = getenv("B200P_PDL_MASK"); return e ? atoi(e) : 0; }();
-static thread_local int g_pdl_class = 0;
-void pdl_set_class(int cls) { g_pdl_class = cls; }
-bool pdl_enabled() { return g_pdl == 1 || (g_pdl_mask & g_pdl_class) != 0; }
-bool pdl_enabled_gemm() { return g_pdl != 0; }
-
-int sm_count() {
-  query_device();
-  return g_sm_count > 0 ? g_sm_count : 148;
-}
-
 }  // namespace b200p
 
 using namespace b200p;
-
-// 0.2: round-2 ABI (PERM8 flags, stream-K / small-matrix GEMM paths, b200p_attn_decode_static, b200p_kv_overflow_count)
-extern "C" const char* b200p_version(void) { return "b200parallm 0.2 (sm_100a)"; }
-extern "C" const char* b200p_last_error(void) { return g_err; }
-
-extern "C" int b200p_arch_check(void) {
-  int rc = query_device();
-  if (rc) return rc;
-  B200P_REQUIRE(g_cc_major == 10, B200P_ERR_ARCH, "device compute capability %d.x is not sm_100", g_cc_major);
-  return B200P_OK;
-}
-
-extern "C" int b200p_sm_count(void) {
-  int rc = query_device();
-  if (rc) return rc;
-  return g_sm_count;
-}
-
-extern "C" int b200p_set_pdl(int enabled) {
-  g_pdl = enabled;
-  return B200P_OK;
-}
 
 extern "C" int b200p_qmm_set_min_tensor_m(int m) {
   B200P_REQUIRE(m >= 1, B200P_ERR_ARG, "min tensor-path M must be >= 1");

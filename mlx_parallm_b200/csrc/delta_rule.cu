@@ -1,0 +1,219 @@
+// Gated delta rule (a linear-attention layer with a per-head matrix state S [dk, dv] that is decayed, corrected towards the
+// current value along the current key and read with the current query), as four kernels over a ragged batch:
+//   delta_prep_kernel         short causal convolution + silu of q, k, v; unit q / k per head; beta and decay   (per token)
+//   delta_conv_commit_kernel  the convolution's carried inputs                                                   (per entry)
+//   delta_scan_kernel         the recurrence, one thread per state column, fp32, token by token                   (per entry, head)
+//   delta_out_kernel          per-head rms norm * weight * silu(gate)                                            (per token)
+// Prompts and single decoded tokens run the SAME scan kernel in the same summation order, so a prompt cut into portions gives
+// the same numbers as one pass.
+#include "common.cuh"
+
+namespace b200p {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+constexpr int DELTA_MAX_TAPS = 16;
+
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* __restrict__ conv_w,
+                  const float* __restrict__ conv_state, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                  const int32_t* __restrict__ t_row, const int32_t* __restrict__ t_pos, const int32_t* __restrict__ t_off,
+                  float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vout, float* __restrict__ beta,
+                  float* __restrict__ decay, int H, int KH, int dk, int dv, int taps) {
+  extern __shared__ float qk[];                      // conv + silu of the q and k channels of this token
+  const int64_t t = blockIdx.x;
+  const int Cqk = 2 * KH * dk, C = Cqk + H * dv;
+  const int row = t_row[t], pos = t_pos[t], off = t_off[t];
+  const float* pt = proj + t * ldp;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {                 // tap j multiplies the input d = taps-1-j tokens back
+      const int d = taps - 1 - j;
+      float in;
+      if (d > pos) in = 0.f;                         // before the sequence
+      else if (d <= off) in = pt[c - (int64_t)d * ldp];
+      else in = conv_state[((int64_t)row * (taps - 1) + (taps - 1 + off - d)) * C + c];
+      acc = fmaf(conv_w[(int64_t)c * taps + j], in, acc);
+    }
+    const float a = silu_f(acc);
+    if (c < Cqk) qk[c] = a;
+    else vout[t * (int64_t)(H * dv) + (c - Cqk)] = a;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int hd = warp; hd < 2 * KH; hd += nw) {       // heads 0..KH-1 of q, then of k
+    const float* src = qk + hd * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    float inv = 1.f / sqrtf(ss + 1e-6f);
+    float* dst;
+    if (hd < KH) { inv *= 1.f / sqrtf((float)dk); dst = qn + t * (int64_t)(KH * dk) + hd * dk; }
+    else dst = kn + t * (int64_t)(KH * dk) + (hd - KH) * dk;
+    for (int i = lane; i < dk; i += 32) dst[i] = src[i] * inv;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    beta[t * H + h] = 1.f / (1.f + expf(-pt[col_b + h]));
+    decay[t * H + h] = expf(-expf(A_log[h]) * softplus_f(pt[col_a + h] + dt_bias[h]));
+  }
+}
+
+__global__ void delta_conv_commit_kernel(const float* __restrict__ proj, int64_t ldp, float* __restrict__ conv_state,
+                                         const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, int64_t C, int taps) {
+  const int e = blockIdx.y;
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = cu[e + 1] - cu[e];
+  if (c >= C || n <= 0) return;
+  float* st = conv_state + (int64_t)rows[e] * (taps - 1) * C + c;
+  float keep[DELTA_MAX_TAPS];
+#pragma unroll
+  for (int i = 0; i < DELTA_MAX_TAPS; ++i) {
+    if (i < taps - 1) {
+      const int rel = n - (taps - 1) + i;            // input i of the new state, counted from the portion's first token
+      keep[i] = rel >= 0 ? proj[((int64_t)cu[e] + rel) * ldp + c] : st[(int64_t)(i + n) * C];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < DELTA_MAX_TAPS; ++i)
+    if (i < taps - 1) st[(int64_t)i * C] = keep[i];
+}
+
+constexpr int DS_CHUNK = 8;       // tokens whose q, k, beta, decay are staged in shared memory at a time
+
+template <int DKP>                // dk padded to 32 / 64 / 128 / 256: one state column per thread, in registers
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
+                  const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
+                  const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ lengths,
+                  float* __restrict__ o, int H, int KH, int dk, int dv) {
+  __shared__ float ks[DS_CHUNK][DKP], qs[DS_CHUNK][DKP], gs[DS_CHUNK], bs[DS_CHUNK];
+  const int e = blockIdx.x, h = blockIdx.y;
+  const int j = blockIdx.z * blockDim.x + threadIdx.x;          // state column
+  const bool live = j < dv;
+  const int t0 = cu[e], t1 = cu[e + 1];
+  if (t1 <= t0) return;
+  const int row = rows[e];
+  const int kh = h / (H / KH);
+  float S[DKP];
+  float* sp = state + (((int64_t)row * H + h) * dk) * dv + j;
+  const bool fresh = lengths[row] == 0;                          // first token of a sequence: the state starts at zero
+#pragma unroll
+  for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < dk) ? sp[(int64_t)i * dv] : 0.f;
+  for (int tc = t0; tc < t1; tc += DS_CHUNK) {
+    const int nt = min(DS_CHUNK, t1 - tc);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * DKP; idx += blockDim.x) {
+      const int tt = idx / DKP, i = idx % DKP;
+      const int64_t src = ((int64_t)(tc + tt) * KH + kh) * dk + i;
+      ks[tt][i] = i < dk ? kn[src] : 0.f;
+      qs[tt][i] = i < dk ? qn[src] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      gs[threadIdx.x] = decay[(int64_t)(tc + threadIdx.x) * H + h];
+      bs[threadIdx.x] = beta[(int64_t)(tc + threadIdx.x) * H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const int64_t vo = ((int64_t)(tc + tt) * H + h) * dv + j;
+      const float vj = live ? v[vo] : 0.f;
+      const float g = gs[tt];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < DKP; ++i) {
+        S[i] *= g;
+        dot = fmaf(S[i], ks[tt][i], dot);
+      }
+      const float u = bs[tt] * (vj - dot);
+      float out = 0.f;
+#pragma unroll
+      for (int i = 0; i < DKP; ++i) {
+        S[i] = fmaf(ks[tt][i], u, S[i]);
+        out = fmaf(S[i], qs[tt][i], out);
+      }
+      if (live) o[vo] = out;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DKP; ++i)
+      if (i < dk) sp[(int64_t)i * dv] = S[i];
+  }
+}
+
+template <typename T>
+__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, int64_t ldp, int64_t col_g,
+                                 const float* __restrict__ norm_w, T* __restrict__ out, int H, int dv, float eps) {
+  const int64_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nw) {
+    const float* src = o + (t * H + h) * dv;
+    const float* g = proj + t * ldp + col_g + (int64_t)h * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32) out[(t * H + h) * dv + i] = Tr<T>::from_f(src[i] * inv * norm_w[i] * silu_f(g[i]));
+  }
+}
+
+}  // namespace b200p
+
+using namespace b200p;
+
+extern "C" int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* conv_w,
+                                const float* conv_state, const float* A_log, const float* dt_bias, const int32_t* t_row,
+                                const int32_t* t_pos, const int32_t* t_off, float* qn, float* kn, float* v, float* beta,
+                                float* decay, int64_t M, int H, int KH, int dk, int dv, int taps, void* stream) {
+  B200P_REQUIRE(proj && conv_w && conv_state && A_log && dt_bias && t_row && t_pos && t_off && qn && kn && v && beta && decay,
+                B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(H > 0 && KH > 0 && H % KH == 0 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
+  B200P_REQUIRE(taps >= 1 && taps <= DELTA_MAX_TAPS, B200P_ERR_ARG, "convolution taps must be in [1, %d]", DELTA_MAX_TAPS);
+  if (M == 0) return B200P_OK;
+  const size_t smem = (size_t)2 * KH * dk * sizeof(float);
+  B200P_REQUIRE(smem <= 48 * 1024, B200P_ERR_ARG, "q and k of one token must fit 48 KB of shared memory");
+  delta_prep_kernel<<<(unsigned)M, 256, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias,
+                                                                      t_row, t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv,
+                                                                      taps);
+  B200P_LAUNCH_CHECK("delta_prep_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_delta_conv_commit(const float* proj, int64_t ldp, float* conv_state, const int32_t* cu, const int32_t* rows,
+                                       int nb, int64_t C, int taps, void* stream) {
+  B200P_REQUIRE(proj && conv_state && cu && rows && nb > 0 && nb < 65536, B200P_ERR_ARG, "null pointer or bad batch");
+  B200P_REQUIRE(taps >= 1 && taps <= DELTA_MAX_TAPS, B200P_ERR_ARG, "convolution taps must be in [1, %d]", DELTA_MAX_TAPS);
+  if (taps == 1) return B200P_OK;
+  dim3 grid((unsigned)((C + 127) / 128), (unsigned)nb);
+  delta_conv_commit_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(proj, ldp, conv_state, cu, rows, C, taps);
+  B200P_LAUNCH_CHECK("delta_conv_commit_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_delta_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay,
+                                float* state, const int32_t* cu, const int32_t* rows, const int32_t* lengths, float* o, int nb,
+                                int H, int KH, int dk, int dv, void* stream) {
+  B200P_REQUIRE(qn && kn && v && beta && decay && state && cu && rows && lengths && o, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(nb > 0 && H > 0 && KH > 0 && H % KH == 0 && H < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
+  B200P_REQUIRE(dk <= 256, B200P_ERR_ARG, "key size %d > 256 is not built", dk);
+  const int threads = dv >= 128 ? 128 : ((dv + 31) / 32) * 32;
+  dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + threads - 1) / threads));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dk <= 32) delta_scan_kernel<32><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 64) delta_scan_kernel<64><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 128) delta_scan_kernel<128><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else delta_scan_kernel<256><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  B200P_LAUNCH_CHECK("delta_scan_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_delta_out(const float* o, const float* proj, int64_t ldp, int64_t col_g, const float* norm_w, void* out,
+                               int64_t M, int H, int dv, float eps, int dtype, void* stream) {
+  B200P_REQUIRE(o && proj && norm_w && out && H > 0 && dv > 0, B200P_ERR_ARG, "null pointer");
+  if (M == 0) return B200P_OK;
+  const unsigned threads = H >= 8 ? 256 : 32 * (unsigned)H;
+  B200P_DISPATCH_DTYPE(dtype, T, (delta_out_kernel<T><<<(unsigned)M, threads, 0, (cudaStream_t)stream>>>(
+      o, proj, ldp, col_g, norm_w, (T*)out, H, dv, eps)));
+  B200P_LAUNCH_CHECK("delta_out_kernel");
+  return B200P_OK;
+}

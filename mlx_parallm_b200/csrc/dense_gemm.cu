@@ -1,0 +1,290 @@
+// Dense (unquantised) linear layers: y[M,N] = x[M,K] . w[N,K]^T with fp32 accumulation, optionally batched over a leading
+// index (one weight block per attention head).  Three kernels behind b200p_gemm:
+//   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles         (rows > GEMV_MAX_M)
+//   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming     (rows <= GEMV_MAX_M: decode)
+//   gemm_simt_kernel   any operand type and any shape or alignment; true fp32 FMA in ascending k for float32 models
+// Epilogues: store in the storage type, store fp32, and the clamped gated unit of b200p.h (gate / up rows interleaved).
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace b200p {
+
+// ---- epilogue -------------------------------------------------------------------------------------------------------
+// value pair (even column n, odd column n+1) of one output row
+template <typename T>
+__device__ __forceinline__ void gemm_store_pair(void* y, int64_t row_off, int64_t n, int64_t N, float v0, float v1, int epi,
+                                                float limit) {
+  if (epi == B200P_GEMM_STORE_F32) {
+    float* p = reinterpret_cast<float*>(y) + row_off;
+    if (n < N) p[n] = v0;
+    if (n + 1 < N) p[n + 1] = v1;
+  } else if (epi == B200P_GEMM_STORE) {
+    T* p = reinterpret_cast<T*>(y) + row_off;
+    if (n < N) p[n] = Tr<T>::from_f(v0);
+    if (n + 1 < N) p[n + 1] = Tr<T>::from_f(v1);
+  } else {  // B200P_GEMM_GLU_CLAMP: v0 = gate, v1 = up of hidden unit n / 2
+    if (n + 1 < N) {
+      const float g = fminf(v0, limit);
+      const float u = fminf(fmaxf(v1, -limit), limit);
+      const float a = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+      reinterpret_cast<T*>(y)[row_off + (n >> 1)] = Tr<T>::from_f(a);
+    }
+  }
+}
+
+// ---- generic kernel ---------------------------------------------------------------------------------------------------
+constexpr int GS_BM = 64, GS_BN = 64, GS_BK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int64_t M, int64_t N, int64_t K,
+                 int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+  __shared__ float xs[GS_BK][GS_BM + 4];
+  __shared__ float ws[GS_BK][GS_BN + 4];
+  const int64_t z = blockIdx.z;
+  x += z * sx;
+  w += z * sw;
+  const int64_t m0 = (int64_t)blockIdx.y * GS_BM, n0 = (int64_t)blockIdx.x * GS_BN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // 4 x 4 outputs: rows ty*4.., columns tx*4..
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int64_t k0 = 0; k0 < K; k0 += GS_BK) {
+    for (int idx = threadIdx.x; idx < GS_BM * GS_BK; idx += 256) {
+      const int r = idx / GS_BK, c = idx % GS_BK;
+      const int64_t m = m0 + r, k = k0 + c;
+      xs[c][r] = (m < M && k < K) ? Tr<T>::to_f(x[m * ldx + k]) : 0.f;
+      const int64_t n = n0 + r;
+      ws[c][r] = (n < N && k < K) ? Tr<T>::to_f(w[n * ldw + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < GS_BK; ++c) {
+      const float4 a = *reinterpret_cast<const float4*>(&xs[c][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&ws[c][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+    const int64_t off = z * sy + m * ldy;
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) gemm_store_pair<T>(y, off, n0 + tx * 4 + j, N, acc[i][j], acc[i][j + 1], epi, limit);
+  }
+}
+
+// ---- tensor-core tile kernel (16-bit operands) ---------------------------------------------------------------------------
+constexpr int GM_BK = 32, GM_PAD = 8, GM_STAGES = 3;
+
+template <typename T, int WM, int WN>     // WM x WN warps, each a 32 x 32 output block
+__global__ void __launch_bounds__(WM * WN * 32)
+gemm_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int64_t M, int64_t N, int64_t K,
+                int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+  constexpr int BM = WM * 32, BN = WN * 32, NT = WM * WN * 32, LDS = GM_BK + GM_PAD;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  T* xs = reinterpret_cast<T*>(smem_raw);                       // [STAGES][BM][LDS]
+  T* ws = xs + GM_STAGES * BM * LDS;                            // [STAGES][BN][LDS]
+  const int64_t z = blockIdx.z;
+  x += z * sx;
+  w += z * sw;
+  const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp / WN, wn = warp % WN;
+  const int nk = (int)((K + GM_BK - 1) / GM_BK);
+
+  auto issue = [&](int kt, int stage) {
+    const int64_t k0 = (int64_t)kt * GM_BK;
+    T* xd = xs + stage * BM * LDS;
+    T* wd = ws + stage * BN * LDS;
+    for (int idx = threadIdx.x; idx < BM * (GM_BK / 8); idx += NT) {
+      const int r = idx / (GM_BK / 8), c = (idx % (GM_BK / 8)) * 8;
+      const bool ok = (m0 + r < M) && (k0 + c < K);
+      cp_async16((uint32_t)__cvta_generic_to_shared(xd + r * LDS + c), ok ? (const void*)(x + (m0 + r) * ldx + k0 + c) : (const void*)x, ok);
+    }
+    for (int idx = threadIdx.x; idx < BN * (GM_BK / 8); idx += NT) {
+      const int r = idx / (GM_BK / 8), c = (idx % (GM_BK / 8)) * 8;
+      const bool ok = (n0 + r < N) && (k0 + c < K);
+      cp_async16((uint32_t)__cvta_generic_to_shared(wd + r * LDS + c), ok ? (const void*)(w + (n0 + r) * ldw + k0 + c) : (const void*)w, ok);
+    }
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < GM_STAGES - 1; ++s) {
+    if (s < nk) issue(s, s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<GM_STAGES - 2>();
+    __syncthreads();
+    if (kt + GM_STAGES - 1 < nk) issue(kt + GM_STAGES - 1, (kt + GM_STAGES - 1) % GM_STAGES);
+    cp_async_commit();
+    const T* xt = xs + (kt % GM_STAGES) * BM * LDS;
+    const T* wt = ws + (kt % GM_STAGES) * BN * LDS;
+#pragma unroll
+    for (int kk = 0; kk < GM_BK; kk += 16) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(xt + (wm * 32 + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8), a[i]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(wt + (wn * 32 + j * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8),
+                b[j]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma16816<T>(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int64_t m = m0 + wm * 32 + i * 16 + (lane >> 2) + hf * 8;
+      if (m >= M) continue;
+      const int64_t off = z * sy + m * ldy;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        gemm_store_pair<T>(y, off, n0 + wn * 32 + j * 8 + (lane & 3) * 2, N, acc[i][j][hf * 2], acc[i][j][hf * 2 + 1], epi, limit);
+    }
+}
+
+// ---- few rows (decode): the weights stream once, every warp owns two weight rows ---------------------------------------------
+constexpr int GEMV_MAX_M = 8;
+
+template <typename T, int MR>
+__global__ void __launch_bounds__(256)
+gemv_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int M, int64_t N, int64_t K, int64_t ldx,
+                 int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+  const int64_t z = blockIdx.z;
+  x += z * sx;
+  w += z * sw;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n = ((int64_t)blockIdx.x * 8 + warp) * 2;
+  if (n >= N) return;
+  const bool two = n + 1 < N;
+  float a0[MR], a1[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) a0[m] = a1[m] = 0.f;
+  const T* w0 = w + n * ldw;
+  const T* w1 = w + (two ? n + 1 : n) * ldw;
+  for (int64_t k = (int64_t)lane * 8; k < K; k += 256) {
+    const uint4 u0 = ldg_stream(w0 + k), u1 = ldg_stream(w1 + k);
+    const T* p0 = reinterpret_cast<const T*>(&u0);
+    const T* p1 = reinterpret_cast<const T*>(&u1);
+    float f0[8], f1[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      f0[e] = Tr<T>::to_f(p0[e]);
+      f1[e] = Tr<T>::to_f(p1[e]);
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      if (m < M) {
+        const uint4 ux = *reinterpret_cast<const uint4*>(x + (int64_t)m * ldx + k);
+        const T* px = reinterpret_cast<const T*>(&ux);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xv = Tr<T>::to_f(px[e]);
+          a0[m] = fmaf(xv, f0[e], a0[m]);
+          a1[m] = fmaf(xv, f1[e], a1[m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m) {
+    a0[m] = warp_sum(a0[m]);
+    a1[m] = warp_sum(a1[m]);
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+      if (m < M) gemm_store_pair<T>(y, z * sy + (int64_t)m * ldy, n, N, a0[m], a1[m], epi, limit);
+  }
+}
+
+template <typename T>
+static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                         int64_t ldy, int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, bool fast_ok,
+                         cudaStream_t st) {
+  const T* xp = (const T*)x;
+  const T* wp = (const T*)w;
+  if (fast_ok && M <= GEMV_MAX_M) {
+    dim3 grid((unsigned)((N + 15) / 16), 1, (unsigned)batch);
+    if (M <= 2) gemv_rows_kernel<T, 2><<<grid, 256, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    else if (M <= 4) gemv_rows_kernel<T, 4><<<grid, 256, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    else gemv_rows_kernel<T, 8><<<grid, 256, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    B200P_LAUNCH_CHECK("gemv_rows_kernel");
+    return B200P_OK;
+  }
+  if (fast_ok) {
+    // 128 x 64 tiles once the grid fills the GPU with them, 64 x 64 below
+    const int64_t big = ((M + 127) / 128) * ((N + 63) / 64) * batch;
+    if (M > 64 && big >= 148) {
+      constexpr int WM = 4, WN = 2;
+      constexpr size_t smem = (size_t)GM_STAGES * (WM * 32 + WN * 32) * (GM_BK + GM_PAD) * sizeof(T);
+      dim3 grid((unsigned)((N + WN * 32 - 1) / (WN * 32)), (unsigned)((M + WM * 32 - 1) / (WM * 32)), (unsigned)batch);
+      gemm_mma_kernel<T, WM, WN><<<grid, WM * WN * 32, smem, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    } else {
+      constexpr int WM = 2, WN = 2;
+      constexpr size_t smem = (size_t)GM_STAGES * (WM * 32 + WN * 32) * (GM_BK + GM_PAD) * sizeof(T);
+      dim3 grid((unsigned)((N + WN * 32 - 1) / (WN * 32)), (unsigned)((M + WM * 32 - 1) / (WM * 32)), (unsigned)batch);
+      gemm_mma_kernel<T, WM, WN><<<grid, WM * WN * 32, smem, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    }
+    B200P_LAUNCH_CHECK("gemm_mma_kernel");
+    return B200P_OK;
+  }
+  dim3 grid((unsigned)((N + GS_BN - 1) / GS_BN), (unsigned)((M + GS_BM - 1) / GS_BM), (unsigned)batch);
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+  B200P_LAUNCH_CHECK("gemm_simt_kernel");
+  return B200P_OK;
+}
+
+}  // namespace b200p
+
+extern "C" int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                          int64_t ldy, int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype,
+                          int epilogue, float limit, void* stream) {
+  using namespace b200p;
+  B200P_REQUIRE(x && w && y, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
+  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_CLAMP, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
+  B200P_REQUIRE(epilogue != B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
+  B200P_REQUIRE((M + 63) / 64 < 65536 && batch < 65536, B200P_ERR_ARG, "grid too large");
+  if (M == 0) return B200P_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the 16-bit fast kernels move 16-byte pieces of rows: every row start and every k step must be 16-byte aligned
+  const bool fast_ok = dtype != B200P_F32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && stride_x % 8 == 0 &&
+                       stride_w % 8 == 0 && aligned(x, 16) && aligned(w, 16);
+  switch (dtype) {
+    case B200P_F32:
+      return gemm_dispatch<float>(x, w, y, M, N, K, ldx, ldw, ldy, batch, stride_x, stride_w, stride_y, epilogue, limit, false, st);
+    case B200P_F16:
+      return gemm_dispatch<__half>(x, w, y, M, N, K, ldx, ldw, ldy, batch, stride_x, stride_w, stride_y, epilogue, limit, fast_ok, st);
+    case B200P_BF16:
+      return gemm_dispatch<__nv_bfloat16>(x, w, y, M, N, K, ldx, ldw, ldy, batch, stride_x, stride_w, stride_y, epilogue, limit,
+                                          fast_ok, st);
+    default:
+      set_error("bad dtype %d", dtype);
+      return B200P_ERR_ARG;
+  }
+}

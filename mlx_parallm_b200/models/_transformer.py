@@ -338,6 +338,24 @@ class DecoderModel:
         """top_p_sampling / categorical(logits / temp) (utils.py:354-361)."""
         ops.sample_top_p(logits, temp, top_p, seed, offset, out=tok_out, probs_out=probs_out)
 
+    supports_ragged = False           # prompts are rectangular [B, L]; left padding is fed like any token (utils.py:473-543)
+    kernel_units = None               # every translation unit of the library (_lib.UNIT_SETS)
+
+    def cache_key(self) -> tuple:
+        """What two models must share for one pooled cache group to serve both (utils._KVPool)."""
+        return (self.head_dim, tuple(l.self_attn.n_kv_heads for l in self.model.layers), id(self))
+
+    def new_cache(self, batch_size: int) -> List[BatchedKVCache]:
+        return [PagedKVCache(self.head_dim, l.self_attn.n_kv_heads, batch_size) for l in self.model.layers]
+
+    def _advance_device(self, cache, a: dict, B: int, ids_i32=None):
+        """End of a decode step on the device: every row took one token."""
+        seen = set()
+        for c in cache:
+            if c._lengths.data_ptr() not in seen:
+                seen.add(c._lengths.data_ptr())
+                ops.advance_lengths(c._lengths, 1)
+
     # -- caches ----------------------------------------------------------------------------------
     def make_cache(self, batch_size: int, step: Optional[int] = None, paged: bool = True) -> List[BatchedKVCache]:
         klass = PagedKVCache if paged else BatchedKVCache
@@ -533,6 +551,32 @@ def prepare_cache(caches: List[BatchedKVCache], B: int, L: int, dtype, device) -
         moved |= c.ensure_capacity(need, dtype, device)
         c.lengths(device)
     return moved
+
+
+def prepare_rows(caches, rows: List[int], counts: List[int], dtype, device) -> bool:
+    """Ragged step: row rows[i] is about to take counts[i] tokens.  Returns True if any buffer moved."""
+    moved = False
+    for c in caches:
+        need = max((c._offsets[r] + n for r, n in zip(rows, counts)), default=0)
+        moved |= c.ensure_capacity(need, dtype, device)
+        c.lengths(device)
+    return moved
+
+
+def advance_rows(caches, rows: List[int], counts: List[int]):
+    """Host mirrors of a ragged step (the device lengths are advanced by the step's own kernel)."""
+    for c in caches:
+        c.advance_rows_host(rows, counts)
+
+
+def release_rows(caches, rows: List[int]):
+    """Give rows back: host offsets and the shared device lengths go to zero; the kernels read position 0 as no history."""
+    seen = set()
+    for c in caches:
+        c.release_rows_host(rows)
+        if c._lengths is not None and c._lengths.data_ptr() not in seen:
+            seen.add(c._lengths.data_ptr())
+            c._sync_lengths()
 
 
 def advance_cache(caches: List[BatchedKVCache], L: int):

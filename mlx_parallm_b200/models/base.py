@@ -6,6 +6,9 @@ Mirrors mlx_parallm/models/base.py (reference):
   PagedKVCache    93-149  adds per-row .offsets_list
   BaseModelArgs   151-161 from_dict drops unknown keys
 
+  RowState / LatentKVCache / DeltaRuleState / TokenState: per-sequence state of layer kinds the reference does not have
+                          (latent attention, gated delta rule, previous-token embedding) under the same row protocol
+
 B200 design: one dense device buffer [B, Hkv, Tcap, D] per layer in the model's 16-bit storage type
 (the reference allocates float32, base.py:111-112 -- deliberate deviation), plus a device
 int32 ``lengths[B]`` the kernels read, so that a captured decode graph stays valid while rows
@@ -21,20 +24,19 @@ from typing import List, Optional
 import torch
 
 
-class BatchedKVCache:
-    def __init__(self, head_dim, n_kv_heads, batch_size=1):
-        self.n_kv_heads = n_kv_heads
-        self.head_dim = head_dim
+class RowState:
+    """Bookkeeping every kind of per-sequence state shares: one row per live sequence, host offsets per row and a device
+    int32 ``lengths[B]`` (one tensor for all layers of a generation) that the kernels read.  On its own it is the entry of
+    a layer that keeps no state (for instance an attention layer that reads another layer's cache)."""
+
+    def __init__(self, batch_size=1):
         self.batch_size = batch_size
-        self.keys: Optional[torch.Tensor] = None
-        self.values: Optional[torch.Tensor] = None
         self.offset = 0
         self.step = 256
         self._offsets: List[int] = [0] * batch_size
         self._lengths: Optional[torch.Tensor] = None     # device int32 [B]; may be shared across layers
         self._lengths_shared = False
 
-    # -- reference surface ------------------------------------------------------------------
     @property
     def offsets(self):
         """Per-row offsets (base.py:87-90 / 141-143)."""
@@ -49,12 +51,18 @@ class BatchedKVCache:
         self._offsets = list(v)
         self._sync_lengths()
 
+    def _drop_buffers(self):
+        """Forget the device buffers (the batch size changed)."""
+
+    def buffers(self) -> tuple:
+        """Device tensors a captured decode step holds pointers to."""
+        return ()
+
     def reset(self, batch_size: int | None = None):
         """base.py:52-64 / 145-148: keep buffers when the batch size is unchanged."""
         if batch_size is not None and batch_size != self.batch_size:
             self.batch_size = batch_size
-            self.keys = None
-            self.values = None
+            self._drop_buffers()
             if not self._lengths_shared:
                 self._lengths = None
         self.offset = 0
@@ -65,6 +73,59 @@ class BatchedKVCache:
                     (self.batch_size,), dtype=torch.int32, device=self._lengths.device)
             else:
                 self._lengths.zero_()          # shared across layers: zeroing it from every layer is idempotent
+
+    @property
+    def capacity(self) -> int:
+        return 0
+
+    def lengths(self, device) -> torch.Tensor:
+        if self._lengths is None:
+            self._lengths = torch.tensor(self._offsets, dtype=torch.int32, device=device)
+        return self._lengths
+
+    def share_lengths(self, t: torch.Tensor):
+        """Let every layer of one generation read (and the step advance) a single lengths tensor."""
+        self._lengths = t
+        self._lengths_shared = True
+
+    def _sync_lengths(self):
+        if self._lengths is not None:
+            self._lengths.copy_(torch.tensor(self._offsets, dtype=torch.int32), non_blocking=False)
+
+    def advance_host(self, L: int):
+        self._offsets = [o + L for o in self._offsets]
+        self.offset = max(self._offsets) if self._offsets else 0
+
+    def advance_rows_host(self, rows: List[int], counts: List[int]):
+        """Ragged step: row rows[i] took counts[i] tokens (the device lengths are advanced by the step itself)."""
+        for r, n in zip(rows, counts):
+            self._offsets[r] += n
+        self.offset = max(self._offsets) if self._offsets else 0
+
+    def release_rows_host(self, rows: List[int]):
+        """Give rows back: their next sequence starts at position 0, which every kernel reads as "no history"."""
+        for r in rows:
+            self._offsets[r] = 0
+        self.offset = max(self._offsets) if self._offsets else 0
+
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        return False
+
+
+class BatchedKVCache(RowState):
+    def __init__(self, head_dim, n_kv_heads, batch_size=1):
+        super().__init__(batch_size)
+        self.n_kv_heads = n_kv_heads
+        self.head_dim = head_dim
+        self.keys: Optional[torch.Tensor] = None
+        self.values: Optional[torch.Tensor] = None
+
+    def _drop_buffers(self):
+        self.keys = None
+        self.values = None
+
+    def buffers(self) -> tuple:
+        return (self.keys, self.values)
 
     def update_and_fetch(self, keys, values):
         """Append [B, Hkv, L, D] at each row's offset and return views up to the max end
@@ -85,24 +146,6 @@ class BatchedKVCache:
     @property
     def capacity(self) -> int:
         return 0 if self.keys is None else self.keys.shape[2]
-
-    def lengths(self, device) -> torch.Tensor:
-        if self._lengths is None:
-            self._lengths = torch.tensor(self._offsets, dtype=torch.int32, device=device)
-        return self._lengths
-
-    def share_lengths(self, t: torch.Tensor):
-        """Let every layer of one generation read (and the step advance) a single lengths tensor."""
-        self._lengths = t
-        self._lengths_shared = True
-
-    def _sync_lengths(self):
-        if self._lengths is not None:
-            self._lengths.copy_(torch.tensor(self._offsets, dtype=torch.int32), non_blocking=False)
-
-    def advance_host(self, L: int):
-        self._offsets = [o + L for o in self._offsets]
-        self.offset = max(self._offsets) if self._offsets else 0
 
     def ensure_capacity(self, needed: int, dtype, device) -> bool:
         """Grow in ``step`` blocks (base.py:68-80 / 104-117).  Returns True if buffers were (re)allocated
@@ -126,6 +169,88 @@ class BatchedKVCache:
                 nk[:, :, :keep] = self.keys[:, :, :keep]
                 nv[:, :, :keep] = self.values[:, :, :keep]
         self.keys, self.values = nk, nv
+        return True
+
+
+class LatentKVCache(RowState):
+    """One low-rank vector per position that serves as key and value of every head of a latent-attention layer (and of the
+    later layers that share it): ``latent [B, Tcap, rank]`` in the model's storage type, grown like the KV buffers above."""
+
+    def __init__(self, rank, batch_size=1):
+        super().__init__(batch_size)
+        self.rank = rank
+        self.latent: Optional[torch.Tensor] = None
+
+    def _drop_buffers(self):
+        self.latent = None
+
+    def buffers(self) -> tuple:
+        return (self.latent,)
+
+    @property
+    def capacity(self) -> int:
+        return 0 if self.latent is None else self.latent.shape[1]
+
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        cap = self.capacity
+        if self.latent is not None and cap >= needed and self.latent.dtype == dtype:
+            return False
+        new_cap = ((needed + self.step - 1) // self.step) * self.step
+        if cap > 0 and self.latent.dtype == dtype:
+            new_cap = max(new_cap, ((cap * 3 // 2 + self.step - 1) // self.step) * self.step)
+        nl = torch.zeros((self.batch_size, new_cap, self.rank), dtype=dtype, device=device)
+        if self.latent is not None and cap > 0 and self.latent.dtype == dtype:
+            keep = min(cap, max(self._offsets) if self._offsets else 0)
+            if keep > 0:
+                nl[:, :keep] = self.latent[:, :keep]
+        self.latent = nl
+        return True
+
+
+class DeltaRuleState(RowState):
+    """State of a gated-delta-rule layer: per row and head the fp32 matrix ``state [B, H, dk, dv]`` and the last
+    ``taps - 1`` inputs of the short convolutions ``conv [B, taps-1, C]`` (fp32).  Constant size per row; never grows."""
+
+    def __init__(self, heads, key_dim, value_dim, conv_channels, taps, batch_size=1):
+        super().__init__(batch_size)
+        self.heads, self.key_dim, self.value_dim = heads, key_dim, value_dim
+        self.conv_channels, self.taps = conv_channels, taps
+        self.state: Optional[torch.Tensor] = None
+        self.conv: Optional[torch.Tensor] = None
+
+    def _drop_buffers(self):
+        self.state = None
+        self.conv = None
+
+    def buffers(self) -> tuple:
+        return (self.state, self.conv)
+
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        if self.state is not None:
+            return False
+        self.state = torch.zeros((self.batch_size, self.heads, self.key_dim, self.value_dim), dtype=torch.float32, device=device)
+        self.conv = torch.zeros((self.batch_size, max(self.taps - 1, 1), self.conv_channels), dtype=torch.float32, device=device)
+        return True
+
+
+class TokenState(RowState):
+    """The last token of every row (``last_token [B]`` int32): what an embedding that looks at the previous token needs
+    when a sequence goes on in a later step."""
+
+    def __init__(self, batch_size=1):
+        super().__init__(batch_size)
+        self.last_token: Optional[torch.Tensor] = None
+
+    def _drop_buffers(self):
+        self.last_token = None
+
+    def buffers(self) -> tuple:
+        return (self.last_token,)
+
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        if self.last_token is not None:
+            return False
+        self.last_token = torch.zeros((self.batch_size,), dtype=torch.int32, device=device)
         return True
 
 

@@ -248,3 +248,118 @@ def sample_top_p(logits, temperature, top_p, seed, offset, out=None, probs_out=N
     _call("b200p_sample_top_p", lambda: lib().b200p_sample_top_p(_p(logits), _p(out), _p(probs_out), B, V, logits.stride(0), float(temperature),
                                    float(top_p), int(seed) & (2**64 - 1), int(offset) & (2**64 - 1), _stream()))
     return out
+
+
+# ---- dense linear layers, ragged batches, gated delta rule, latent attention ------------------------------------------
+def gemm(x, w, epilogue=_lib.GEMM_STORE, out=None, limit=0.0, batch=1, strides=(0, 0, 0), M=None, N=None, K=None,
+         ldx=None, ldw=None, ldy=None):
+    """y = x . w^T with fp32 accumulation (b200p_gemm).  Plain call: x [M, K], w [N, K] of one dtype.  Batched call (one
+    weight block per head): pass M, N, K, the row strides and ``strides`` = element strides of x, w, y between products."""
+    _dev(x, w, out)
+    assert x.dtype == w.dtype and x.stride(-1) == 1 and w.stride(-1) == 1
+    if M is None:
+        M, K = x.shape
+        N = w.shape[0]
+        assert w.shape[1] == K, (tuple(x.shape), tuple(w.shape))
+        ldx, ldw = x.stride(0), w.stride(0)
+    if out is None:
+        n_out = N // 2 if epilogue == _lib.GEMM_GLU_CLAMP else N
+        out = torch.empty((M, n_out * batch), dtype=torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype, device=x.device)
+    if ldy is None:
+        ldy = out.stride(0)
+    want = torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype
+    assert out.dtype == want and out.stride(-1) == 1, (out.dtype, want)
+    _call(("b200p_gemm", N, K), lambda: lib().b200p_gemm(_p(x), _p(w), _p(out), M, N, K, ldx, ldw, ldy, batch, strides[0], strides[1],
+                                                        strides[2], dtype_code(x.dtype), epilogue, float(limit), _stream()))
+    return out
+
+
+def ragged_plan(cu, rows, lengths, t_row, t_pos, t_off, nb: int, M: int):
+    _dev(cu, rows, lengths, t_row, t_pos, t_off)
+    _call("b200p_ragged_plan", lambda: lib().b200p_ragged_plan(_p(cu), _p(rows), _p(lengths), _p(t_row), _p(t_pos), _p(t_off), nb, M,
+                                                              _stream()))
+
+
+def ragged_advance(lengths, last_token, ids, cu, rows, nb: int):
+    _dev(lengths, last_token, ids, cu, rows)
+    _call("b200p_ragged_advance", lambda: lib().b200p_ragged_advance(_p(lengths), _p(last_token), _p(ids), _p(cu), _p(rows), nb, _stream()))
+
+
+def embed_hashed(ids, t_row, t_pos, t_off, last_token, embed, bigram, h, scale, buckets=0, mul_prev=0, mul_cur=0):
+    _dev(ids, t_row, t_pos, t_off, last_token, embed, bigram, h)
+    M = ids.numel()
+    V, W = embed.shape
+    assert h.dtype == torch.float32 and h.shape[1] == W and (bigram is None or bigram.shape == (buckets + 1, W))
+    _call("b200p_embed_hashed", lambda: lib().b200p_embed_hashed(_p(ids), _p(t_row), _p(t_pos), _p(t_off), _p(last_token), _p(embed),
+                                                                _p(bigram), _p(h), M, W, V, float(scale), int(buckets), int(mul_prev),
+                                                                int(mul_cur), dtype_code(embed.dtype), _stream()))
+    return h
+
+
+def norm_add_norm(h, eps, dtype, y=None, w_post=None, w_next=None, x_out=None, raw_out=None):
+    """h += rms_norm(y) * w_post; raw_out = h; x_out = rms_norm(h) * w_next (each part optional; b200p_norm_add_norm)."""
+    _dev(h, y, w_post, w_next, x_out, raw_out)
+    M, W = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous()
+    for t in (y, w_post, w_next):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    for t in (x_out, raw_out):
+        assert t is None or (t.dtype == dtype and t.is_contiguous())
+    _call("b200p_norm_add_norm", lambda: lib().b200p_norm_add_norm(_p(y), _p(w_post), _p(h), _p(w_next), _p(x_out), _p(raw_out), M, W,
+                                                                  float(eps), dtype_code(dtype), _stream()))
+
+
+def token_gate(gate, table, ids, out, col0: int):
+    _dev(gate, table, ids, out)
+    M, d = gate.shape
+    assert gate.dtype == torch.float32 and gate.is_contiguous() and out.is_contiguous() and out.dtype == table.dtype
+    _call("b200p_token_gate", lambda: lib().b200p_token_gate(_p(gate), _p(table), _p(ids), _p(out), M, d, table.stride(0), int(col0),
+                                                            dtype_code(table.dtype), _stream()))
+    return out
+
+
+def delta_prep(proj, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps):
+    _dev(proj, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay)
+    M = proj.shape[0]
+    _call("b200p_delta_prep", lambda: lib().b200p_delta_prep(_p(proj), proj.stride(0), int(col_b), int(col_a), _p(conv_w), _p(conv_state),
+                                                            _p(A_log), _p(dt_bias), _p(t_row), _p(t_pos), _p(t_off), _p(qn), _p(kn), _p(v),
+                                                            _p(beta), _p(decay), M, H, KH, dk, dv, taps, _stream()))
+
+
+def delta_conv_commit(proj, conv_state, cu, rows, nb: int, C: int, taps: int):
+    _dev(proj, conv_state, cu, rows)
+    _call("b200p_delta_conv_commit", lambda: lib().b200p_delta_conv_commit(_p(proj), proj.stride(0), _p(conv_state), _p(cu), _p(rows), nb,
+                                                                          C, taps, _stream()))
+
+
+def delta_scan(qn, kn, v, beta, decay, state, cu, rows, lengths, o, nb, H, KH, dk, dv):
+    _dev(qn, kn, v, beta, decay, state, cu, rows, lengths, o)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    _call("b200p_delta_scan", lambda: lib().b200p_delta_scan(_p(qn), _p(kn), _p(v), _p(beta), _p(decay), _p(state), _p(cu), _p(rows),
+                                                            _p(lengths), _p(o), nb, H, KH, dk, dv, _stream()))
+
+
+def delta_out(o, proj, col_g, norm_w, out, H, dv, eps):
+    _dev(o, proj, norm_w, out)
+    M = o.shape[0]
+    _call("b200p_delta_out", lambda: lib().b200p_delta_out(_p(o), _p(proj), proj.stride(0), int(col_g), _p(norm_w), _p(out), M, H, dv,
+                                                          float(eps), dtype_code(out.dtype), _stream()))
+
+
+def latent_prep(proj, q_rank, kv_rank, wq, wkv, eps, cq_out, cache, t_row, t_pos):
+    """``cache`` [rows, Tcap, kv_rank] or None for a layer that reads another layer's latents (kv_rank 0)."""
+    _dev(proj, wq, wkv, cq_out, cache, t_row, t_pos)
+    M = proj.shape[0]
+    Tcap = 0 if cache is None else cache.shape[1]
+    _call("b200p_latent_prep", lambda: lib().b200p_latent_prep(_p(proj), proj.stride(0), q_rank, kv_rank if cache is not None else 0,
+                                                              _p(wq), _p(wkv), float(eps), _p(cq_out), _p(cache), Tcap, _p(t_row),
+                                                              _p(t_pos), M, dtype_code(cq_out.dtype), _stream()))
+
+
+def latent_attn(q, cache, t_row, t_pos, out, H, R, window, scale):
+    _dev(q, cache, t_row, t_pos, out)
+    M = q.shape[0]
+    assert q.dtype == torch.float32 and q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and out.dtype == cache.dtype
+    _call("b200p_latent_attn", lambda: lib().b200p_latent_attn(_p(q), _p(cache), cache.shape[1], _p(t_row), _p(t_pos), _p(out), M, H, R,
+                                                              int(window), float(scale), dtype_code(cache.dtype), _stream()))
+    return out

@@ -32,7 +32,7 @@ import numpy as np
 import torch
 
 from . import ops, sample_utils
-from .models._transformer import DecoderModel, advance_cache, bind_cache_group, prepare_cache
+from .models._transformer import DecoderModel, advance_cache, advance_rows, bind_cache_group, prepare_cache, prepare_rows
 from .models.base import BatchedKVCache, PagedKVCache
 from .sample_utils import top_p_sampling
 from .tokenizer_utils import TokenizerWrapper, load_tokenizer
@@ -48,7 +48,11 @@ class ModelNotFoundError(Exception):
 
 def _get_classes(config: dict):
     """utils.py:47-67."""
-    model_type = MODEL_REMAPPING.get(config["model_type"], config["model_type"])
+    # designs without an HF ``model_type`` name themselves by ``architecture`` (models/dogulorn.py)
+    model_type = config.get("model_type") or str(config.get("architecture", "")).lower()
+    if not model_type:
+        raise ValueError("config.json names neither model_type nor architecture")
+    model_type = MODEL_REMAPPING.get(model_type, model_type)
     try:
         arch = importlib.import_module(f"mlx_parallm_b200.models.{model_type}")
     except ImportError:
@@ -136,7 +140,7 @@ class _KVPool:
             paged: bool = True, device=None, owner: int = 0) -> List[BatchedKVCache]:
         """``step`` sizes the FIRST allocation of a new entry and the growth quantum of a reused one; a reused entry keeps
         its (possibly larger) buffers, so the decode graph captured over them stays valid across calls."""
-        key = (head_dim, tuple(kv_heads), batch_size, owner, threading.get_ident())
+        key = ((head_dim, tuple(kv_heads), owner), batch_size, threading.get_ident())     # = get_for of a DecoderModel
         with self._mu:
             caches = self._pool.get(key)
             if caches is None:
@@ -153,18 +157,37 @@ class _KVPool:
                 c.step = step
         return caches
 
+    def get_for(self, model, batch_size: int, *, step: Optional[int] = None) -> list:
+        """Cache group of ``model``'s own making (``model.new_cache``: KV buffers, latents, recurrent state, whatever its
+        layers carry), pooled per model, batch size and thread like ``get``.  A reused group comes back reset: every row at
+        position 0."""
+        key = (model.cache_key(), batch_size, threading.get_ident())
+        with self._mu:
+            caches = self._pool.get(key)
+            if caches is None:
+                caches = model.new_cache(batch_size)
+                bind_cache_group(caches, model.device, step)
+                if len(self._pool) > 16:
+                    self._pool.clear()
+                self._pool[key] = caches
+                return caches
+        for c in caches:
+            c.reset(batch_size)
+            if step is not None:
+                c.step = step
+        return caches
+
 
 def _presized_cache(model: DecoderModel, B: int, total_tokens: int) -> List[BatchedKVCache]:
     """Pool entry whose buffers take ``total_tokens`` per row in ONE allocation (rounded to 256 like utils.py:1234), so a
     generation of known length never re-allocates or copies its KV cache and its decode graph is captured once."""
     step = max(256, ((int(total_tokens) + 255) // 256) * 256)
-    kv_heads = [l.self_attn.n_kv_heads for l in model.layers]
-    return _kv_pool.get(model.head_dim, kv_heads, B, step=step, paged=True, device=model.device, owner=id(model))
+    return _kv_pool.get_for(model, B, step=step)
 
 
 def _presize(kwargs: dict, model: DecoderModel, prompt_tokens, max_tokens: int) -> dict:
     """generate_step kwargs with a cache that already holds prompt + max_tokens positions (unless the caller brought one)."""
-    if kwargs.get("cache") is None and isinstance(model, DecoderModel):
+    if kwargs.get("cache") is None and hasattr(model, "new_cache"):
         B, L = prompt_tokens.shape
         kwargs = dict(kwargs, cache=_presized_cache(model, B, L + max_tokens))
     return kwargs
@@ -179,6 +202,7 @@ class _DecodeStep:
 
     def __init__(self, model: DecoderModel, cache: List[BatchedKVCache], B: int, greedy: bool, use_graph: bool = True):
         self.model, self.cache, self.B, self.greedy = model, cache, B, greedy
+        self.rows: Optional[List[int]] = None      # ragged models: the cache rows this step's B entries continue (None: 0..B-1)
         dev = model.device
         self.tok = torch.zeros((B,), dtype=torch.int32, device=dev)
         self.probs = torch.zeros((B,), dtype=torch.float32, device=dev)
@@ -190,7 +214,20 @@ class _DecodeStep:
         self._sig = None
 
     def _signature(self):
-        return tuple((c.keys.data_ptr(), c.values.data_ptr(), c._lengths.data_ptr()) for c in self.cache)
+        return tuple(tuple(0 if t is None else t.data_ptr() for t in c.buffers()) + (c._lengths.data_ptr(),) for c in self.cache)
+
+    def set_rows(self, rows: List[int]):
+        """Ragged models only: entry i of the next steps continues cache row rows[i] (a batch whose shorter requests have
+        ended keeps stepping the others).  The row list is a device buffer the captured graph reads, so changing it does not
+        re-capture."""
+        if not getattr(self.model, "supports_ragged", False):
+            raise NotImplementedError("this model steps every row of its cache")
+        rows = [int(r) for r in rows]
+        if len(rows) != self.B or len(set(rows)) != self.B:
+            raise ValueError("one distinct cache row per entry")
+        with self.model._lock:
+            self.rows = rows
+            self.arena["rows"].copy_(torch.tensor(rows, dtype=torch.int32))
 
     def _body(self):
         m = self.model
@@ -199,11 +236,7 @@ class _DecodeStep:
             m._head(None, self.arena, logits_out=self.logits, x_rows=self.arena["x"])
         else:
             m._head(self.arena["h"], self.arena, logits_out=self.logits)
-        seen = set()
-        for c in self.cache:
-            if c._lengths.data_ptr() not in seen:
-                seen.add(c._lengths.data_ptr())
-                ops.advance_lengths(c._lengths, 1)
+        m._advance_device(self.cache, self.arena, self.B, self.tok)
         if self.greedy:
             m.greedy_tokens(self.logits, self.tok, self.probs)
 
@@ -212,10 +245,16 @@ class _DecodeStep:
         model's forward lock: the scratch arena and the GEMM workspace belong to one step at a time, and a capture must
         not see another thread's launches (capture_error_mode thread_local: other threads may allocate meanwhile)."""
         with self.model._lock:
-            moved = prepare_cache(self.cache, self.B, 1, self.model.dtype, self.model.device)
+            rows = self.rows
+            if rows is None:
+                moved = prepare_cache(self.cache, self.B, 1, self.model.dtype, self.model.device)
+            else:
+                moved = prepare_rows(self.cache, rows, [1] * self.B, self.model.dtype, self.model.device)
             arena = self.model._arena(self.B, self.B)     # same object unless the model dropped / re-keyed its arenas
             stale = arena is not self.arena
             self.arena = arena
+            if stale and rows is not None:
+                arena["rows"].copy_(torch.tensor(rows, dtype=torch.int32))
             if not self.use_graph:
                 self._body()
             else:
@@ -241,8 +280,11 @@ class _DecodeStep:
                     self.graph, self._sig = g, sig
                     # capture does not execute: replay below performs the step
                 self.graph.replay()
-            for c in self.cache:
-                c.advance_host(1)
+            if rows is None:
+                for c in self.cache:
+                    c.advance_host(1)
+            else:
+                advance_rows(self.cache, rows, [1] * self.B)
 
 
 DecodeSession = _DecodeStep      # public name: one replayable decode step over a model + cache group
@@ -272,13 +314,16 @@ def generate_step(
     top_p: float = 1.0,
     logit_bias: Optional[Dict[int, float]] = None,
     cache: Optional[List[BatchedKVCache]] = None,
+    prompt_lengths: Optional[List[int]] = None,
 ) -> Generator[Tuple[torch.Tensor, torch.Tensor], None, None]:
     """Generator yielding (tokens [B,1] int64, probs [B,1] float32) forever (utils.py:315-427).
 
     Same contract as the reference: prefill on the whole (left-padded) prompt batch, greedy if temp == 0
     else top-p / categorical sampling, repetition_penalty raises NotImplementedError (utils.py:366-367),
     and the step for token n+1 is already in flight when token n is yielded (utils.py:420-427).
-    ``probs`` is per row (the reference gathers row 0 only)."""
+    ``probs`` is per row (the reference gathers row 0 only).  ``prompt_lengths`` (models with ``supports_ragged``
+    only): row b's last prompt_lengths[b] ids are its prompt, the ids before them are left padding and are not fed at all, so a
+    row's tokens do not depend on the other rows of the batch."""
     if repetition_penalty:
         raise NotImplementedError("repetition_penalty not supported.")
     dev = model.device
@@ -286,9 +331,10 @@ def generate_step(
     if y.dim() == 1:
         y = y[None, :]
     B = y.shape[0]
-    kv_heads = [l.self_attn.n_kv_heads for l in model.layers]
+    if prompt_lengths is not None and not getattr(model, "supports_ragged", False):
+        raise NotImplementedError("prompt_lengths needs a model that takes ragged batches; this one feeds left padding as tokens")
     if cache is None:
-        cache = _kv_pool.get(model.head_dim, kv_heads, B, paged=True, device=dev, owner=id(model))   # utils.py:390-394
+        cache = _kv_pool.get_for(model, B)                                                           # utils.py:390-394
     elif cache and cache[0]._lengths is None:
         bind_cache_group(cache, dev)
     greedy = temp == 0
@@ -320,13 +366,16 @@ def generate_step(
                                f"{fx.status()}): results of this generation are invalid")
         # same boundary, same reason: a row appended beyond its cache capacity is dropped by the kernel (it cannot happen
         # through prepare_cache, which grows the buffers first -- this is the loud failure if that invariant ever breaks)
-        dropped = ops.kv_overflow_count(reset=True)
+        dropped = ops.kv_overflow_count(reset=True) if model.kernel_units is None else 0
         if dropped:
             raise RuntimeError(f"KV cache overflow: {dropped} (token, head) appends were dropped by b200p_rope_kv_append; "
                                "results of this generation are invalid")
 
     # prefill (eager, chunked) + first sample
-    logits = model(y, cache=cache, last_only=True)[:, -1, :]
+    if prompt_lengths is not None:
+        logits = model(y, cache=cache, last_only=True, prompt_lengths=prompt_lengths)[:, -1, :]
+    else:
+        logits = model(y, cache=cache, last_only=True)[:, -1, :]
     sample(logits)
     check_exchange()
     out_y = step.tok.to(torch.int64).view(B, 1)
@@ -423,7 +472,10 @@ def batch_generate(model, tokenizer, prompts: List[str], max_tokens: int = 100, 
     if tokenizer.pad_token is None:
         tokenizer._tokenizer.pad_token = tokenizer.eos_token
         tokenizer._tokenizer.pad_token_id = tokenizer.eos_token_id
-    prompts_toks = torch.tensor(tokenizer._tokenizer(prompts_fm, padding=True)["input_ids"])
+    enc = tokenizer._tokenizer(prompts_fm, padding=True)
+    prompts_toks = torch.tensor(enc["input_ids"])
+    if getattr(model, "supports_ragged", False) and "attention_mask" in enc and "prompt_lengths" not in kwargs:
+        kwargs = dict(kwargs, prompt_lengths=[int(sum(m)) for m in enc["attention_mask"]])      # padding is skipped, not fed
     tic = time.perf_counter()
     output_toks = []
     prompt_time = 0.0
@@ -544,8 +596,7 @@ async def batch_generate_text(model, tokenizer, prompts: List[str], max_tokens: 
         suffixes = [s[lcp:] for s in seqs]
         est = max((len(s) for s in suffixes), default=0)
         desired = max(256, min(8192, int(((est + max_tokens) // 256 + 1) * 256)))       # utils.py:1234
-        kv_heads = [l.self_attn.n_kv_heads for l in model.layers]
-        caches = _kv_pool.get(model.head_dim, kv_heads, B, step=desired, paged=True, device=model.device, owner=id(model))
+        caches = _kv_pool.get_for(model, B, step=desired)
         if lcp > 0 and not disable_prefix_cache:
             lcp_ids = torch.tensor(np.tile(np.array(seqs[0][:lcp], dtype=np.int64), (B, 1)))
             model(lcp_ids, cache=caches, last_only=True)                                 # utils.py:1254-1259
@@ -595,10 +646,12 @@ def load_config(model_path: Path) -> dict:
 
 
 def load_model(model_path: Path, lazy: bool = False, model_config: dict = {}, device="cuda",
-               tp_rank: int = 0, tp_world: int = 1) -> DecoderModel:
+               tp_rank: int = 0, tp_world: int = 1, dtype=None) -> DecoderModel:
     """utils.py:630-708: config.json -> arch classes -> safetensors (MLX layout) -> quantized modules.
     Only tensors that exist as module parameters are taken (utils.py:693-699).  With tp_world > 1 each
-    rank keeps its column / row shard (tp.shard_weights)."""
+    rank keeps its column / row shard (tp.shard_weights).  Model families with dense weights (``Model.dense``: no
+    ``quantization`` block) load their matrices in ``dtype`` (a torch dtype or its name; default: as stored); a family that
+    names its translation units (``Model.kernel_units``) gets them compiled on a checkout without a built library."""
     model_path = Path(model_path)
     config = load_config(model_path)
     config.update(model_config)
@@ -613,8 +666,12 @@ def load_model(model_path: Path, lazy: bool = False, model_config: dict = {}, de
             for k in f.keys():
                 weights[k] = f.get_tensor(k)
     model_class, model_args_class = _get_classes(config)
-    if "quantization" not in config:
-        raise ValueError("only MLX-quantized checkpoints (config['quantization']) are on this build's hot path")
+    dense = getattr(model_class, "dense", False)
+    if not dense and "quantization" not in config:
+        raise ValueError("only MLX-quantized checkpoints (config['quantization']) are on this model family's hot path")
+    if getattr(model_class, "kernel_units", None) is not None:
+        from . import _lib
+        _lib.ensure_built(model_class.kernel_units)
     model = model_class(model_args_class.from_dict(config))
     if hasattr(model, "sanitize"):
         weights = model.sanitize(weights)
@@ -624,9 +681,14 @@ def load_model(model_path: Path, lazy: bool = False, model_config: dict = {}, de
         logging.warning(f"Filtering out {len(dropped)} unmatched weight tensors during load.")
     weights = {k: v for k, v in weights.items() if k in known}
     if tp_world > 1:
+        if dense:
+            raise NotImplementedError("tensor parallelism is not built for this model family")
         from . import tp
         weights = tp.shard_weights(weights, config, tp_rank, tp_world)
-    model.load_weights(weights, device=device)
+    if dense:
+        model.load_weights(weights, device=device, dtype=getattr(torch, dtype) if isinstance(dtype, str) else dtype)
+    else:
+        model.load_weights(weights, device=device)
     return model
 
 
