@@ -436,6 +436,140 @@ def cpu_reference(cfg_name, B, T, steps=3, warmup=1, budget_layers=2, seed=1234)
             "ms_per_step_full_model": t_step * 1e3}
 
 
+# ------------------------------------------------------------------------------------------ design comparison (--design)
+DESIGN_SIZES = {
+    # name: width, ff, layers, heads, head_dim, q_rank, kv_rank, window, delta heads / kv heads / key / value size
+    "1b-layers": dict(width=2048, ff=8192, n_layers=3, heads=16, head_dim=128, q_rank=768, kv_rank=256, window=512,
+                      delta_heads=16, delta_kv_heads=8, delta_dim=128, delta_vdim=128),
+    "8b-layers": dict(width=4096, ff=14336, n_layers=3, heads=32, head_dim=128, q_rank=1536, kv_rank=512, window=1024,
+                      delta_heads=32, delta_kv_heads=8, delta_dim=128, delta_vdim=128),
+}
+
+
+def _profile_eager(fn, reps=2):
+    """CUDA events around every launch of ``fn`` (eager, no graph): {kernel key: mean ms per call, calls per run}."""
+    import torch
+    from mlx_parallm_b200 import ops
+    fn()
+    torch.cuda.synchronize()
+    ops.PROFILER = {}
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    prof, ops.PROFILER = ops.PROFILER, None
+    return {k: {"calls": len(v) // reps, "mean_us": sum(a.elapsed_time(b) for a, b in v) / len(v) * 1e3} for k, v in prof.items()}
+
+
+def _gemm_rooflines(prof, rows, w_bytes_per_el, tflops, hbm_gbs):
+    """For every GEMM key 'name[N=..,K=..]' of a profile: achieved fraction of max(FLOP time, byte time) at ``rows`` rows."""
+    import re
+    out = {}
+    for k, v in prof.items():
+        m = re.match(r"(b200p_gemm|b200p_qmm)\[N=(\d+),K=(\d+)\]", k)
+        if not m:
+            continue
+        N, K = int(m.group(2)), int(m.group(3))
+        flop_us = 2.0 * rows * N * K / (tflops * 1e12) * 1e6
+        byte_us = (N * K * w_bytes_per_el + rows * (K + N) * 2) / (hbm_gbs * 1e9) * 1e6
+        out[k] = {"mean_us": round(v["mean_us"], 2), "calls": v["calls"], "roofline_us": round(max(flop_us, byte_us), 2),
+                  "frac": round(max(flop_us, byte_us) / v["mean_us"], 3), "bound": "tensor" if flop_us > byte_us else "hbm"}
+    return out
+
+
+def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_decode=32, T_ctx=1024):
+    """Prefill and decode throughput of the design at layer sizes of real models (random weights, few layers), beside the
+    Llama graph of this framework at equal width / feed-forward / head count (4-bit weights, its usual format)."""
+    import torch
+    from mlx_parallm_b200 import _lib, ops, synth
+    from mlx_parallm_b200.utils import DecodeSession, _get_classes
+    assert design == "dogulorn"
+    _lib.require_device()
+    hbm, src = peaks()
+    pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    tflops = float(pk.get("bf16_tflops", 1590.0))
+    dev = "cuda:0"
+    rows_out = []
+    for name in sizes:
+        sz = DESIGN_SIZES[name]
+        res = {"size": name, "dims": sz}
+        # ---- the design
+        cfg = synth.dogulorn_config(**sz)
+        w = synth.dogulorn_random_weights(cfg, device=dev)
+        Model, Args = _get_classes(cfg)
+        model = Model(Args.from_dict(cfg)).load_weights(w, device=dev)
+        del w
+        torch.cuda.empty_cache()
+        g = torch.Generator(device=dev)
+        g.manual_seed(3)
+        prompts = torch.randint(0, cfg["vocab"], (B_prefill, L_prefill), generator=g, device=dev).tolist()
+
+        def prefill():
+            cache = model.make_cache(B_prefill, step=L_prefill + 8)
+            return model.forward_ragged(prompts, cache)
+        for _ in range(2):
+            prefill()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            prefill()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        res["prefill"] = {"batch": B_prefill, "prompt_len": L_prefill, "ms": min(ts), "tok_s": B_prefill * L_prefill / min(ts) * 1e3}
+        res["prefill_kernels"] = _profile_eager(prefill, reps=1)
+        res["prefill_gemm_roofline"] = _gemm_rooflines(res["prefill_kernels"], B_prefill * L_prefill, 2, tflops, hbm)
+        cache = model.make_cache(B_decode, step=T_ctx + steps + warmup + 64)
+        ctx = torch.randint(0, cfg["vocab"], (B_decode, T_ctx), generator=g, device=dev).tolist()
+        model.forward_ragged(ctx, cache)
+        sess = DecodeSession(model, cache, B_decode, greedy=True)
+        sess.tok.copy_(torch.randint(0, cfg["vocab"], (B_decode,), generator=g, device=dev, dtype=torch.int32))
+        ms = time_steps(sess, steps, warmup)
+        res["decode"] = {"batch": B_decode, "context": T_ctx, "ms_per_step": ms, "tok_s": B_decode / ms * 1e3}
+        kp, launches = kernel_profile(sess, steps=2)
+        res["decode_kernels"] = {k: {"calls": v["calls_per_step"], "mean_us": round(v["mean_ms"] * 1e3, 2)} for k, v in kp.items()}
+        res["decode_launches_per_step"] = launches
+        res["decode_gemm_roofline"] = _gemm_rooflines({k: {"calls": v["calls_per_step"], "mean_us": v["mean_ms"] * 1e3} for k, v in kp.items()},
+                                                      B_decode, 2, tflops, hbm)
+        del model, cache, sess
+        torch.cuda.empty_cache()
+        # ---- the closest existing graph at equal size
+        lcfg = dict(model_type="llama", hidden_size=sz["width"], num_hidden_layers=sz["n_layers"], intermediate_size=sz["ff"],
+                    num_attention_heads=sz["heads"], num_key_value_heads=max(1, sz["heads"] // 4), rms_norm_eps=1e-5,
+                    vocab_size=cfg["vocab"], rope_theta=500000.0, tie_word_embeddings=False,
+                    quantization=dict(group_size=64, bits=4))
+        lw = synth.random_weights(lcfg, dtype="float16", device=dev)
+        LModel, LArgs = _get_classes(lcfg)
+        lm = LModel(LArgs.from_dict(lcfg)).load_weights(lw, device=dev)
+        del lw
+        torch.cuda.empty_cache()
+        ref = {"prefill": time_prefill(lm, lcfg, B_prefill, L_prefill, reps=3)}
+        lids = torch.randint(0, lcfg["vocab_size"], (B_prefill, L_prefill), generator=g, device=dev)
+
+        def lprefill():
+            return lm(lids, cache=lm.make_cache(B_prefill, step=L_prefill + 8), last_only=True)
+        lp = _profile_eager(lprefill, reps=1)
+        ref["prefill_gemm_roofline"] = _gemm_rooflines(lp, B_prefill * L_prefill, 0.5 + 4.0 / 64, tflops, hbm)
+        ref["prefill_kernels"] = {k: {"calls": v["calls"], "mean_us": round(v["mean_us"], 2)} for k, v in lp.items()}
+        lcache, lsess = make_session(lm, B_decode, T_ctx, steps + warmup + 64)
+        lms = time_steps(lsess, steps, warmup)
+        ref["decode"] = {"batch": B_decode, "context": T_ctx, "ms_per_step": lms, "tok_s": B_decode / lms * 1e3}
+        lkp, _ = kernel_profile(lsess, steps=2)
+        ref["decode_kernels"] = {k: {"calls": v["calls_per_step"], "mean_us": round(v["mean_ms"] * 1e3, 2)} for k, v in lkp.items()}
+        ref["decode_gemm_roofline"] = _gemm_rooflines({k: {"calls": v["calls_per_step"], "mean_us": v["mean_ms"] * 1e3} for k, v in lkp.items()},
+                                                      B_decode, 0.5 + 4.0 / 64, tflops, hbm)
+        res["llama_equal_size"] = ref
+        for k in ("prefill_kernels",):
+            res[k] = {kk: {"calls": v["calls"], "mean_us": round(v["mean_us"], 2)} for kk, v in res[k].items()}
+        rows_out.append(res)
+        del lm, lcache, lsess
+        torch.cuda.empty_cache()
+    return {"metric": "design_throughput", "design": design, "dtype": "bf16 matrices / f32 residual, norms, recurrence",
+            "data": "synthetic (random-init weights, random token ids)", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src},
+            "sizes": rows_out}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -446,6 +580,10 @@ def main():
     ap.add_argument("--sweep", default=",".join(DEFAULT_SWEEP), help="comma list of extra workloads ('' = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--design", default=None, choices=["dogulorn"],
+                    help="instead of the headline workload: prefill / decode throughput of this design at real layer sizes, "
+                         "beside the Llama graph at equal size (one JSON line of its own shape)")
+    ap.add_argument("--design-sizes", default=",".join(DESIGN_SIZES))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -459,6 +597,10 @@ def main():
     def emit(line: dict):
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     cfg_name, B, T = WORKLOADS[args.workload]
+
+    if args.design is not None:
+        emit(design_compare(args.design, [x for x in args.design_sizes.split(",") if x], min(args.steps, 64), args.warmup))
+        return
 
     if args.impl == "reference":
         if rank != 0:

@@ -202,3 +202,92 @@ def save_checkpoint(path: str, cfg: dict, weights: Dict[str, torch.Tensor]):
         v = v.detach().cpu().contiguous()
         tensors[k] = v.view(torch.uint32) if v.dtype == torch.int32 else v
     save_file(tensors, os.path.join(path, "model.safetensors"), metadata={"format": "mlx"})
+
+
+# ---- Dogulorn (models/dogulorn.py): dense bfloat16 checkpoints, tensors l<i>.<part> ---------------------------------------
+def dogulorn_config(width: int, ff: int, n_layers: int, heads: int, head_dim: int, q_rank: int, kv_rank: int, window: int,
+                    delta_heads: int, delta_kv_heads: int, delta_dim: int, delta_vdim: int, vocab: int = 32000, taps: int = 4,
+                    side_dim: int = 64, buckets: int = 65521) -> dict:
+    """A config of the design at the sizes of a real model: layers cycle (delta, attention, attention reading the previous
+    attention layer's latents); every layer has the feed-forward."""
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    layers, last_own = [], None
+    for i in range(n_layers):
+        kind = i % 3
+        if kind == 0:
+            layers.append({"type": "delta", "mlp": dict(mlp), "mixer": {"heads": delta_heads, "kv_heads": delta_kv_heads,
+                                                                      "dim": delta_dim, "vdim": delta_vdim, "conv": taps}})
+            continue
+        m = {"heads": heads, "dim": head_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank, "mask": {"size": window},
+             "scale": head_dim ** -0.5}
+        if kind == 2 and last_own is not None:
+            m["kv_from"] = last_own
+        else:
+            last_own = i
+        layers.append({"type": "latent_attention", "mlp": dict(mlp), "mixer": m})
+    return {"architecture": "Dogulorn", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": buckets, "mul_prev": 31, "mul_cur": 7}},
+            "token_side": {"dim": side_dim}}
+
+
+def dogulorn_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Shape of every tensor of a Dogulorn checkpoint (matrices [out, in])."""
+    W, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    big = (cfg.get("embedding") or {}).get("bigram")
+    if big:
+        out["bigram"] = (big["buckets"] + 1, W)
+    side = cfg.get("token_side")
+    if side:
+        out["side.embed"] = (V, len(cfg["layers"]) * side["dim"])
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out[p + "norm1"] = out[p + "norm1b"] = (W,)
+        if L["type"] == "delta":
+            H, G, dk, dv, n = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"], m.get("conv", 1)
+            for nm, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                out[p + "mix." + nm] = (rows, W)
+                out[p + f"mix.{nm}.conv"] = (rows, n)
+            out[p + "mix.b"] = out[p + "mix.a"] = (H, W)
+            out[p + "mix.g"] = (H * dv, W)
+            out[p + "mix.o"] = (W, H * dv)
+            out[p + "mix.A_log"] = out[p + "mix.dt_bias"] = (H,)
+            out[p + "mix.norm"] = (dv,)
+        else:
+            H, dk, dv, rq, rk = m["heads"], m["dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            out[p + "mix.dq"], out[p + "mix.dq.norm"], out[p + "mix.uq"] = (rq, W), (rq,), (H * dk, rq)
+            if m.get("kv_from") is None:
+                out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = (rk, W), (rk,)
+            out[p + "mix.uk"], out[p + "mix.uv"], out[p + "mix.o"] = (H * dk, rk), (H * dv, rk), (W, H * dv)
+        if L.get("mlp") is not None:
+            ff = L["mlp"]["ff"]
+            out[p + "norm2"] = out[p + "norm2b"] = (W,)
+            out[p + "mlp.gate"] = out[p + "mlp.up"] = (ff, W)
+            out[p + "mlp.down"] = (W, ff)
+        if side:
+            out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = (side["dim"], W), (W, side["dim"]), (W,)
+    return out
+
+
+def dogulorn_random_weights(cfg: dict, seed: int = 1234, device="cpu") -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors: matrices N(0, 1/in), norm weights 1 + N(0, 0.02), decay parameters spread so that heads forget at
+    different speeds.  One generator per tensor, seeded from (seed, name)."""
+    dev = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in dogulorn_shapes(cfg).items():
+        g = torch.Generator(device=dev)
+        g.manual_seed(_stable_seed(seed, name))
+        if len(shape) == 2 and not name.endswith(".conv"):
+            t = torch.randn(shape, generator=g, device=dev) / math.sqrt(shape[1])
+            if name in ("embed", "bigram", "side.embed"):
+                t = t * math.sqrt(shape[1]) * 0.5
+        elif name.endswith(".conv"):
+            t = torch.randn(shape, generator=g, device=dev) * 0.5
+        elif name.endswith("A_log"):
+            t = torch.rand(shape, generator=g, device=dev) * 3.0 - 2.0
+        elif name.endswith("dt_bias"):
+            t = torch.randn(shape, generator=g, device=dev)
+        else:
+            t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
+        out[name] = t.to(torch.bfloat16)
+    return out

@@ -197,12 +197,18 @@ _kv_pool = _KVPool()
 
 
 # --------------------------------------------------------------------------------- decode graph
+import itertools
+
+_step_ids = itertools.count(1)
+
+
 class _DecodeStep:
     """One decode step as a replayable CUDA graph over static buffers."""
 
     def __init__(self, model: DecoderModel, cache: List[BatchedKVCache], B: int, greedy: bool, use_graph: bool = True):
         self.model, self.cache, self.B, self.greedy = model, cache, B, greedy
         self.rows: Optional[List[int]] = None      # ragged models: the cache rows this step's B entries continue (None: 0..B-1)
+        self._uid = next(_step_ids)
         dev = model.device
         self.tok = torch.zeros((B,), dtype=torch.int32, device=dev)
         self.probs = torch.zeros((B,), dtype=torch.float32, device=dev)
@@ -227,7 +233,7 @@ class _DecodeStep:
             raise ValueError("one distinct cache row per entry")
         with self.model._lock:
             self.rows = rows
-            self.arena["rows"].copy_(torch.tensor(rows, dtype=torch.int32))
+            self.arena["rows_owner"] = None        # rewritten by the next run()
 
     def _body(self):
         m = self.model
@@ -253,8 +259,11 @@ class _DecodeStep:
             arena = self.model._arena(self.B, self.B)     # same object unless the model dropped / re-keyed its arenas
             stale = arena is not self.arena
             self.arena = arena
-            if stale and rows is not None:
-                arena["rows"].copy_(torch.tensor(rows, dtype=torch.int32))
+            if "rows" in arena and arena.get("rows_owner") != self._uid:
+                # the scratch arena (and the row list in it that the captured graph reads) belongs to the model and is shared by
+                # every decode step of this batch size, whatever cache group it steps: write this step's rows before it runs
+                arena["rows"].copy_(torch.tensor(rows if rows is not None else list(range(self.B)), dtype=torch.int32))
+                arena["rows_owner"] = self._uid
             if not self.use_graph:
                 self._body()
             else:
