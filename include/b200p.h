@@ -337,6 +337,14 @@ int b200p_latent_prep(const float* proj, int64_t ldp, int q_rank, int kv_rank, c
  * fp32 softmax of q . c_j * scale; out [M, H, R] (dtype) = sum_j p_j c_j.  R <= 512. */
 int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, void* out,
                       int64_t M, int H, int R, int64_t window, float scale, int dtype, void* stream);
+/* The same attention on the tensor cores: tiles of 16 consecutive tokens of one entry and one head (max_n = the longest
+ * entry's token count), or, when max_n == 1 (a decode step), tiles of 16 heads of each entry's one token; 16-bit types,
+ * R % 32 == 0, R <= 512 (b200p_latent_attn_tiles_supported says whether a call
+ * qualifies).  q and p are rounded to the storage type for the products; max, sum and the accumulators are fp32. */
+int b200p_latent_attn_tiles_supported(int R, int dtype);
+int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
+                            const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
+                            int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -79,17 +79,20 @@ __global__ void delta_conv_commit_kernel(const float* __restrict__ proj, int64_t
     if (i < taps - 1) st[(int64_t)i * C] = keep[i];
 }
 
-constexpr int DS_CHUNK = 8;       // tokens whose q, k, beta, decay are staged in shared memory at a time
+constexpr int DS_CHUNK = 8;       // tokens whose q, k, v, beta, decay are staged in shared memory at a time
+constexpr int DS_THREADS = 128;   // state columns per CTA (threads past dv only help with the staging)
 
 template <int DKP>                // dk padded to 32 / 64 / 128 / 256: one state column per thread, in registers
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ lengths,
                   float* __restrict__ o, int H, int KH, int dk, int dv) {
-  __shared__ float ks[DS_CHUNK][DKP], qs[DS_CHUNK][DKP], gs[DS_CHUNK], bs[DS_CHUNK];
+  constexpr int PF = DS_CHUNK * DKP / DS_THREADS;                // q / k elements each thread stages per chunk
+  __shared__ __align__(16) float ks[2][DS_CHUNK][DKP], qs[2][DS_CHUNK][DKP];
+  __shared__ float vs[2][DS_CHUNK][DS_THREADS], gs[2][DS_CHUNK], bs[2][DS_CHUNK];
   const int e = blockIdx.x, h = blockIdx.y;
-  const int j = blockIdx.z * blockDim.x + threadIdx.x;          // state column
+  const int j = blockIdx.z * DS_THREADS + threadIdx.x;           // state column
   const bool live = j < dv;
   const int t0 = cu[e], t1 = cu[e + 1];
   if (t1 <= t0) return;
@@ -100,39 +103,73 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   const bool fresh = lengths[row] == 0;                          // first token of a sequence: the state starts at zero
 #pragma unroll
   for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < dk) ? sp[(int64_t)i * dv] : 0.f;
-  for (int tc = t0; tc < t1; tc += DS_CHUNK) {
+  // The next chunk's inputs are fetched into registers while the current chunk runs out of shared memory, then parked in the
+  // other buffer: the recurrence never waits for global memory.
+  float pk[PF], pq[PF], pv[DS_CHUNK], pg = 0.f, pb = 0.f;
+  auto fetch = [&](int tc) {
     const int nt = min(DS_CHUNK, t1 - tc);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * DKP; idx += blockDim.x) {
-      const int tt = idx / DKP, i = idx % DKP;
+#pragma unroll
+    for (int r = 0; r < PF; ++r) {
+      const int idx = threadIdx.x + r * DS_THREADS, tt = idx / DKP, i = idx % DKP;
+      const bool ok = tt < nt && i < dk;
       const int64_t src = ((int64_t)(tc + tt) * KH + kh) * dk + i;
-      ks[tt][i] = i < dk ? kn[src] : 0.f;
-      qs[tt][i] = i < dk ? qn[src] : 0.f;
+      pk[r] = ok ? kn[src] : 0.f;
+      pq[r] = ok ? qn[src] : 0.f;
     }
+#pragma unroll
+    for (int tt = 0; tt < DS_CHUNK; ++tt) pv[tt] = (live && tt < nt) ? v[((int64_t)(tc + tt) * H + h) * dv + j] : 0.f;
     if (threadIdx.x < nt) {
-      gs[threadIdx.x] = decay[(int64_t)(tc + threadIdx.x) * H + h];
-      bs[threadIdx.x] = beta[(int64_t)(tc + threadIdx.x) * H + h];
+      pg = decay[(int64_t)(tc + threadIdx.x) * H + h];
+      pb = beta[(int64_t)(tc + threadIdx.x) * H + h];
     }
-    __syncthreads();
+  };
+  auto park = [&](int buf) {
+#pragma unroll
+    for (int r = 0; r < PF; ++r) {
+      const int idx = threadIdx.x + r * DS_THREADS;
+      ks[buf][idx / DKP][idx % DKP] = pk[r];
+      qs[buf][idx / DKP][idx % DKP] = pq[r];
+    }
+#pragma unroll
+    for (int tt = 0; tt < DS_CHUNK; ++tt) vs[buf][tt][threadIdx.x] = pv[tt];
+    if (threadIdx.x < DS_CHUNK) { gs[buf][threadIdx.x] = pg; bs[buf][threadIdx.x] = pb; }
+  };
+  fetch(t0);
+  park(0);
+  __syncthreads();
+  int buf = 0;
+  for (int tc = t0; tc < t1; tc += DS_CHUNK, buf ^= 1) {
+    const int nt = min(DS_CHUNK, t1 - tc);
+    const bool more = tc + DS_CHUNK < t1;
+    if (more) fetch(tc + DS_CHUNK);
     for (int tt = 0; tt < nt; ++tt) {
-      const int64_t vo = ((int64_t)(tc + tt) * H + h) * dv + j;
-      const float vj = live ? v[vo] : 0.f;
-      const float g = gs[tt];
-      float dot = 0.f;
+      const float vj = vs[buf][tt][threadIdx.x];
+      const float g = gs[buf][tt];
+      // both reductions run as four interleaved partial sums (i mod 4), always combined in the same order: four times shorter
+      // dependency chains, and the same numbers whether a token arrives in a prompt or alone
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DKP; ++i) {
-        S[i] *= g;
-        dot = fmaf(S[i], ks[tt][i], dot);
+      for (int i = 0; i < DKP; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[buf][tt][i]);
+        S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
+        d4[0] = fmaf(S[i], k4.x, d4[0]); d4[1] = fmaf(S[i + 1], k4.y, d4[1]);
+        d4[2] = fmaf(S[i + 2], k4.z, d4[2]); d4[3] = fmaf(S[i + 3], k4.w, d4[3]);
       }
-      const float u = bs[tt] * (vj - dot);
-      float out = 0.f;
+      const float u = bs[buf][tt] * (vj - ((d4[0] + d4[1]) + (d4[2] + d4[3])));
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DKP; ++i) {
-        S[i] = fmaf(ks[tt][i], u, S[i]);
-        out = fmaf(S[i], qs[tt][i], out);
+      for (int i = 0; i < DKP; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[buf][tt][i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[buf][tt][i]);
+        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
+        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
+        o4[0] = fmaf(S[i], q4.x, o4[0]); o4[1] = fmaf(S[i + 1], q4.y, o4[1]);
+        o4[2] = fmaf(S[i + 2], q4.z, o4[2]); o4[3] = fmaf(S[i + 3], q4.w, o4[3]);
       }
-      if (live) o[vo] = out;
+      if (live) o[((int64_t)(tc + tt) * H + h) * dv + j] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     }
+    if (more) park(buf ^ 1);          // the other buffer was last read in the previous iteration, before its closing barrier
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
@@ -196,7 +233,7 @@ extern "C" int b200p_delta_scan(const float* qn, const float* kn, const float* v
   B200P_REQUIRE(qn && kn && v && beta && decay && state && cu && rows && lengths && o, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(nb > 0 && H > 0 && KH > 0 && H % KH == 0 && H < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dk <= 256, B200P_ERR_ARG, "key size %d > 256 is not built", dk);
-  const int threads = dv >= 128 ? 128 : ((dv + 31) / 32) * 32;
+  const int threads = DS_THREADS;
   dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + threads - 1) / threads));
   cudaStream_t st = (cudaStream_t)stream;
   if (dk <= 32) delta_scan_kernel<32><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);

@@ -1,7 +1,8 @@
 // Dense (unquantised) linear layers: y[M,N] = x[M,K] . w[N,K]^T with fp32 accumulation, optionally batched over a leading
-// index (one weight block per attention head).  Three kernels behind b200p_gemm:
-//   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles         (rows > GEMV_MAX_M)
-//   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming     (rows <= GEMV_MAX_M: decode)
+// index (one weight block per attention head).  Four kernels behind b200p_gemm:
+//   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles, two tile shapes      (more than 64 rows)
+//   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..64 rows: decode)
+//   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming                  (up to 8 rows)
 //   gemm_simt_kernel   any operand type and any shape or alignment; true fp32 FMA in ascending k for float32 models
 // Epilogues: store in the storage type, store fp32, and the clamped gated unit of b200p.h (gate / up rows interleaved).
 #include "common.cuh"
@@ -83,88 +84,112 @@ gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restr
 }
 
 // ---- tensor-core tile kernel (16-bit operands) ---------------------------------------------------------------------------
-constexpr int GM_BK = 32, GM_PAD = 8, GM_STAGES = 3;
+// WM x WN warps, each a WTM x WTN output block (multiples of 16), k tiles of BK staged by cp.async STAGES deep.  Two shapes
+// are instantiated: 128 x 128 (warp blocks of 64 x 64: four MMAs per ldmatrix) for prompts and 64 x 64 when that grid would
+// not fill the GPU.
+constexpr int GM_PAD = 8;
 
-template <typename T, int WM, int WN>     // WM x WN warps, each a 32 x 32 output block
+template <typename T, int WM, int WN, int WTM, int WTN, int BK, int STAGES>
 __global__ void __launch_bounds__(WM * WN * 32)
 gemm_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int64_t M, int64_t N, int64_t K,
                 int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
-  constexpr int BM = WM * 32, BN = WN * 32, NT = WM * WN * 32, LDS = GM_BK + GM_PAD;
+  constexpr int BM = WM * WTM, BN = WN * WTN, NT = WM * WN * 32, LDS = BK + GM_PAD, MI = WTM / 16, NJ = WTN / 8;
+  static_assert(WTM % 16 == 0 && WTN % 16 == 0 && BK % 16 == 0, "warp blocks are made of 16 x 16 pieces");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);                       // [STAGES][BM][LDS]
-  T* ws = xs + GM_STAGES * BM * LDS;                            // [STAGES][BN][LDS]
+  T* ws = xs + STAGES * BM * LDS;                               // [STAGES][BN][LDS]
   const int64_t z = blockIdx.z;
   x += z * sx;
   w += z * sw;
   const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wm = warp / WN, wn = warp % WN;
-  const int nk = (int)((K + GM_BK - 1) / GM_BK);
+  const int nk = (int)((K + BK - 1) / BK);
 
   auto issue = [&](int kt, int stage) {
-    const int64_t k0 = (int64_t)kt * GM_BK;
+    const int64_t k0 = (int64_t)kt * BK;
     T* xd = xs + stage * BM * LDS;
     T* wd = ws + stage * BN * LDS;
-    for (int idx = threadIdx.x; idx < BM * (GM_BK / 8); idx += NT) {
-      const int r = idx / (GM_BK / 8), c = (idx % (GM_BK / 8)) * 8;
+    for (int idx = threadIdx.x; idx < BM * (BK / 8); idx += NT) {
+      const int r = idx / (BK / 8), c = (idx % (BK / 8)) * 8;
       const bool ok = (m0 + r < M) && (k0 + c < K);
       cp_async16((uint32_t)__cvta_generic_to_shared(xd + r * LDS + c), ok ? (const void*)(x + (m0 + r) * ldx + k0 + c) : (const void*)x, ok);
     }
-    for (int idx = threadIdx.x; idx < BN * (GM_BK / 8); idx += NT) {
-      const int r = idx / (GM_BK / 8), c = (idx % (GM_BK / 8)) * 8;
+    for (int idx = threadIdx.x; idx < BN * (BK / 8); idx += NT) {
+      const int r = idx / (BK / 8), c = (idx % (BK / 8)) * 8;
       const bool ok = (n0 + r < N) && (k0 + c < K);
       cp_async16((uint32_t)__cvta_generic_to_shared(wd + r * LDS + c), ok ? (const void*)(w + (n0 + r) * ldw + k0 + c) : (const void*)w, ok);
     }
   };
 
-  float acc[2][4][4];
+  float acc[MI][NJ][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
 
 #pragma unroll
-  for (int s = 0; s < GM_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < nk) issue(s, s);
     cp_async_commit();
   }
   for (int kt = 0; kt < nk; ++kt) {
-    cp_async_wait<GM_STAGES - 2>();
+    cp_async_wait<STAGES - 2>();
     __syncthreads();
-    if (kt + GM_STAGES - 1 < nk) issue(kt + GM_STAGES - 1, (kt + GM_STAGES - 1) % GM_STAGES);
+    if (kt + STAGES - 1 < nk) issue(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
-    const T* xt = xs + (kt % GM_STAGES) * BM * LDS;
-    const T* wt = ws + (kt % GM_STAGES) * BN * LDS;
+    const T* xt = xs + (kt % STAGES) * BM * LDS;
+    const T* wt = ws + (kt % STAGES) * BN * LDS;
 #pragma unroll
-    for (int kk = 0; kk < GM_BK; kk += 16) {
-      uint32_t a[2][4], b[2][4];
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t a[MI][4], b[NJ / 2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
-        ldsm_x4((uint32_t)__cvta_generic_to_shared(xt + (wm * 32 + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8), a[i]);
+      for (int i = 0; i < MI; ++i)
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(xt + (wm * WTM + i * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8), a[i]);
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        ldsm_x4((uint32_t)__cvta_generic_to_shared(wt + (wn * 32 + j * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8),
+      for (int j = 0; j < NJ / 2; ++j)
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(wt + (wn * WTN + j * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8),
                 b[j]);
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < MI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma16816<T>(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+        for (int j = 0; j < NJ; ++j) mma16816<T>(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
     }
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      const int64_t m = m0 + wm * 32 + i * 16 + (lane >> 2) + hf * 8;
+      const int64_t m = m0 + wm * WTM + i * 16 + (lane >> 2) + hf * 8;
       if (m >= M) continue;
       const int64_t off = z * sy + m * ldy;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        gemm_store_pair<T>(y, off, n0 + wn * 32 + j * 8 + (lane & 3) * 2, N, acc[i][j][hf * 2], acc[i][j][hf * 2 + 1], epi, limit);
+      for (int j = 0; j < NJ; ++j)
+        gemm_store_pair<T>(y, off, n0 + wn * WTN + j * 8 + (lane & 3) * 2, N, acc[i][j][hf * 2], acc[i][j][hf * 2 + 1], epi, limit);
     }
+}
+
+template <typename T, int WM, int WN, int WTM, int WTN, int BK, int STAGES>
+static int gemm_mma_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
+                           int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st) {
+  constexpr int BM = WM * WTM, BN = WN * WTN;
+  constexpr size_t smem = (size_t)STAGES * (BM + BN) * (BK + GM_PAD) * sizeof(T);
+  auto kern = gemm_mma_kernel<T, WM, WN, WTM, WTN, BK, STAGES>;
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm_mma_kernel)");
+      attr_set = true;
+    }
+  }
+  dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
+  kern<<<grid, WM * WN * 32, smem, st>>>(x, w, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+  B200P_LAUNCH_CHECK("gemm_mma_kernel");
+  return B200P_OK;
 }
 
 // ---- few rows (decode): the weights stream once, every warp owns two weight rows ---------------------------------------------
@@ -222,6 +247,77 @@ gemv_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restr
   }
 }
 
+// ---- decode batches (9..64 rows): weights stream straight from global memory into MMA fragments ----------------------------
+// A CTA owns 16 weight rows (two n8 tiles) and splits K over its 8 warps (2 n-tiles x 4 k-slices); a warp walks its slice 32
+// elements at a time: every lane loads 16 contiguous bytes of "its" weight row (row lane/4, the quarter lane%4 of the 32) and
+// the same 16 bytes of its activation rows, and uses them as the k pairs of two m16n8k16 MMAs.  The MMA sums over k in whatever
+// order the pairs are presented, as long as A and B present the same one, so no shared memory, ldmatrix or transposition is
+// needed and every row is read in 64-byte pieces.  The four k-slices are summed through shared memory in a fixed order.
+constexpr int GK_SLICES = 4, GK_THREADS = 256;
+
+template <typename T, int MT>     // MT m16 tiles: rows <= 16 * MT
+__global__ void __launch_bounds__(GK_THREADS)
+gemm_stream_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int M, int64_t N, int64_t K, int64_t ldx,
+                   int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+  __shared__ float red[GK_SLICES][2][MT][32][4];
+  const int64_t z = blockIdx.z;
+  x += z * sx;
+  w += z * sw;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = warp & 1, ks = warp >> 1;
+  const int64_t n_row = (int64_t)blockIdx.x * 16 + nt * 8 + (lane >> 2);
+  const bool n_ok = n_row < N;
+  const T* wp = w + (n_ok ? n_row : 0) * ldw + (lane & 3) * 8;
+  const T* xp[MT][2];
+  bool x_ok[MT][2];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int m = i * 16 + (lane >> 2) + hf * 8;
+      x_ok[i][hf] = m < M;
+      xp[i][hf] = x + (int64_t)(x_ok[i][hf] ? m : 0) * ldx + (lane & 3) * 8;
+    }
+  float acc[MT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  // slice ks takes the 32-element blocks ks, ks + 4, ...: neighbouring warps read neighbouring 64-byte pieces of a row
+#pragma unroll 4
+  for (int64_t k = (int64_t)ks * 32; k < K; k += 32 * GK_SLICES) {
+    const bool k_ok = k + (lane & 3) * 8 < K;                    // K % 8 == 0: a 16-byte piece is inside or outside
+    uint4 b = make_uint4(0, 0, 0, 0);
+    if (n_ok && k_ok) b = ldg_stream(wp + k);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
+      if (x_ok[i][0] && k_ok) a0 = *reinterpret_cast<const uint4*>(xp[i][0] + k);
+      if (x_ok[i][1] && k_ok) a1 = *reinterpret_cast<const uint4*>(xp[i][1] + k);
+      const uint32_t f0[4] = {a0.x, a1.x, a0.y, a1.y}, f1[4] = {a0.z, a1.z, a0.w, a1.w};
+      mma16816<T>(acc[i], f0, b.x, b.y);
+      mma16816<T>(acc[i], f1, b.z, b.w);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) red[ks][nt][i][lane][e] = acc[i][e];
+  __syncthreads();
+  if (ks != 0) return;
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = ((red[0][nt][i][lane][e] + red[1][nt][i][lane][e]) + red[2][nt][i][lane][e]) + red[3][nt][i][lane][e];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int m = i * 16 + (lane >> 2) + hf * 8;
+      if (m < M)
+        gemm_store_pair<T>(y, z * sy + (int64_t)m * ldy, (int64_t)blockIdx.x * 16 + nt * 8 + (lane & 3) * 2, N, v[hf * 2], v[hf * 2 + 1],
+                           epi, limit);
+    }
+  }
+}
+
 template <typename T>
 static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
                          int64_t ldy, int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, bool fast_ok,
@@ -237,21 +333,18 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
     return B200P_OK;
   }
   if (fast_ok) {
-    // 128 x 64 tiles once the grid fills the GPU with them, 64 x 64 below
-    const int64_t big = ((M + 127) / 128) * ((N + 63) / 64) * batch;
-    if (M > 64 && big >= 148) {
-      constexpr int WM = 4, WN = 2;
-      constexpr size_t smem = (size_t)GM_STAGES * (WM * 32 + WN * 32) * (GM_BK + GM_PAD) * sizeof(T);
-      dim3 grid((unsigned)((N + WN * 32 - 1) / (WN * 32)), (unsigned)((M + WM * 32 - 1) / (WM * 32)), (unsigned)batch);
-      gemm_mma_kernel<T, WM, WN><<<grid, WM * WN * 32, smem, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
-    } else {
-      constexpr int WM = 2, WN = 2;
-      constexpr size_t smem = (size_t)GM_STAGES * (WM * 32 + WN * 32) * (GM_BK + GM_PAD) * sizeof(T);
-      dim3 grid((unsigned)((N + WN * 32 - 1) / (WN * 32)), (unsigned)((M + WM * 32 - 1) / (WM * 32)), (unsigned)batch);
-      gemm_mma_kernel<T, WM, WN><<<grid, WM * WN * 32, smem, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+    if (M <= 64) {
+      dim3 grid((unsigned)((N + 15) / 16), 1, (unsigned)batch);
+      if (M <= 16) gemm_stream_kernel<T, 1><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+      else if (M <= 32) gemm_stream_kernel<T, 2><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+      else gemm_stream_kernel<T, 4><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+      B200P_LAUNCH_CHECK("gemm_stream_kernel");
+      return B200P_OK;
     }
-    B200P_LAUNCH_CHECK("gemm_mma_kernel");
-    return B200P_OK;
+    // 128 x 128 tiles once that grid covers most of the GPU's SMs, 64 x 64 below
+    const int64_t big = ((M + 127) / 128) * ((N + 127) / 128) * batch;
+    if (big >= 96) return gemm_mma_launch<T, 2, 2, 64, 64, 32, 4>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
+    return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
   }
   dim3 grid((unsigned)((N + GS_BN - 1) / GS_BN), (unsigned)((M + GS_BM - 1) / GS_BM), (unsigned)batch);
   gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);

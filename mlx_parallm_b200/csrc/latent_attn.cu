@@ -3,7 +3,12 @@
 // so the cache is read as it is stored.  A sliding window bounds the visible positions.
 //   latent_prep_kernel   rms norms of the two down-projections; the key/value latent goes into the cache
 //   latent_attn_kernel   one CTA per token and group of heads; keys staged 32 at a time in shared memory; online fp32 softmax
+//                        (decode steps, float32 models, ranks off the tensor-core shapes)
+//   latent_attn_tile_kernel  16-bit models: a tile of 16 query rows per CTA (prompts: 16 consecutive tokens of one sequence for
+//                        one head; decode steps: 16 heads of the one new token, which all read the same keys), mma.sync
+//                        m16n8k16 for q.c and p.c over 64-key chunks staged once for both products
 #include "common.cuh"
+#include "mma_util.cuh"
 
 namespace b200p {
 
@@ -103,6 +108,151 @@ latent_attn_kernel(const float* __restrict__ q, const T* __restrict__ cache, int
   }
 }
 
+
+// ---- prompts on the tensor cores -----------------------------------------------------------------------------------------
+// CTA = (tile of 16 tokens of entry e, head h), 4 warps.  Per chunk of 64 positions of the latent cache (staged by cp.async,
+// one copy serves keys and values):
+//   S   warp w: scores of its 16 keys, q [16, R] x c[16 keys, R]^T                     -> shared S [16, 64] fp32, masked
+//   P   8 threads per row: running max / sum in fp32, p = exp(s - max) as 16-bit       -> shared P [16, 64]
+//   O   warp w: columns [w R/4, (w+1) R/4) of o [16, R] += P x c[64 keys, its columns]   (accumulators rescaled first)
+constexpr int LT_ROWS = 16, LT_KEYS = 64, LT_THREADS = 128, LT_MAX_NT = 16;      // R <= 512, R % 32 == 0
+
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS)
+latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache, int64_t Tcap, const int32_t* __restrict__ cu,
+                        const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos, T* __restrict__ out, int H, int R,
+                        int64_t window, float scale, int by_head) {
+  extern __shared__ __align__(128) uint8_t lt_smem[];
+  // by_head == 0: rows of the tile are 16 consecutive tokens of entry e = blockIdx.z, for head blockIdx.y (prompts)
+  // by_head == 1: rows are 16 consecutive heads of the ONE token of entry e (decode: every head reads the same keys)
+  const int e = blockIdx.z;
+  const int h = by_head ? blockIdx.y * LT_ROWS : blockIdx.y;
+  const int t0 = by_head ? cu[e] : cu[e] + blockIdx.x * LT_ROWS;
+  const int nrow = by_head ? (cu[e + 1] > cu[e] ? min(LT_ROWS, H - h) : 0) : min(LT_ROWS, cu[e + 1] - t0);    // live rows
+  if (nrow <= 0) return;
+  const int tstep = by_head ? 0 : 1, hstep = by_head ? 1 : 0;   // row r is token t0 + r * tstep, head h + r * hstep
+  const int LDC = R + 8;                                         // padded rows: ldmatrix reads 8 rows without bank conflicts
+  T* cs = reinterpret_cast<T*>(lt_smem);                         // [64][LDC]
+  T* qs = cs + LT_KEYS * LDC;                                    // [16][LDC]
+  T* ps = qs + LT_ROWS * LDC;                                    // [16][72]
+  float* ss = reinterpret_cast<float*>(ps + LT_ROWS * 72);       // [16][68]
+  float* row_m = ss + LT_ROWS * 68;                              // running max, sum, and this chunk's rescale factor
+  float* row_l = row_m + LT_ROWS;
+  float* row_c = row_l + LT_ROWS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t p0 = t_pos[t0];                                  // positions of the tile's rows are p0, p0 + 1, ...
+  const int64_t plast = by_head ? p0 : p0 + nrow - 1;
+  const int64_t kmin = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  const T* cbase = cache + (int64_t)rows[e] * Tcap * R;
+  for (int idx = threadIdx.x; idx < LT_ROWS * R; idx += LT_THREADS) {
+    const int r = idx / R, c = idx % R;
+    qs[r * LDC + c] = Tr<T>::from_f(r < nrow ? q[((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R + c] : 0.f);
+  }
+  if (threadIdx.x < LT_ROWS) { row_m[threadIdx.x] = -INFINITY; row_l[threadIdx.x] = 0.f; }
+  const int ntw = R / 32;                                        // 8-column tiles of o per warp
+  float o[LT_MAX_NT][4];
+#pragma unroll
+  for (int i = 0; i < LT_MAX_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int chunks_per_row = R / 8;
+  for (int64_t j0 = kmin; j0 <= plast; j0 += LT_KEYS) {
+    __syncthreads();                                             // the previous chunk's products are done with cs / ss / ps
+    for (int idx = threadIdx.x; idx < LT_KEYS * chunks_per_row; idx += LT_THREADS) {
+      const int kk = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
+      const bool ok = j0 + kk <= plast;
+      cp_async16((uint32_t)__cvta_generic_to_shared(cs + kk * LDC + c), ok ? (const void*)(cbase + (j0 + kk) * R + c) : (const void*)cbase, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    {   // ---- S
+      float sc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+      for (int kk = 0; kk < R; kk += 16) {
+        uint32_t a[4], b[4];
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(qs + (lane & 15) * LDC + kk + (lane >> 4) * 8), a);
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(cs + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * LDC + kk + ((lane >> 3) & 1) * 8), b);
+        mma16816<T>(sc[0], a, b[0], b[1]);
+        mma16816<T>(sc[1], a, b[2], b[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int el = 0; el < 4; ++el) {
+          const int r = (lane >> 2) + (el >> 1) * 8;
+          const int kc = warp * 16 + nt * 8 + (lane & 3) * 2 + (el & 1);
+          const int64_t key = j0 + kc, pr = p0 + r * tstep;
+          const bool vis = r < nrow && key <= pr && (window <= 0 || pr - key < window);
+          ss[r * 68 + kc] = vis ? sc[nt][el] * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    {   // ---- P: thread = (row, eighth of the chunk)
+      const int r = threadIdx.x >> 3, seg = threadIdx.x & 7;
+      float v[8], mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v[i] = ss[r * 68 + seg * 8 + i]; mx = fmaxf(mx, v[i]); }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float mo = row_m[r], mn = fmaxf(mo, mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float pv = mn == -INFINITY ? 0.f : __expf(v[i] - mn);      // masked scores are -inf: exp gives 0
+        sum += pv;
+        ps[r * 72 + seg * 8 + i] = Tr<T>::from_f(pv);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      __syncwarp();                                              // every lane of the row has read row_m before it changes
+      if (seg == 0) {
+        const float corr = mn == -INFINITY ? 1.f : __expf(mo - mn);      // mo = -inf on the first visible chunk: 0
+        row_c[r] = corr;
+        row_l[r] = row_l[r] * corr + sum;
+        row_m[r] = mn;
+      }
+    }
+    __syncthreads();
+    {   // ---- O
+      const float c0 = row_c[lane >> 2], c1 = row_c[(lane >> 2) + 8];
+#pragma unroll
+      for (int i = 0; i < LT_MAX_NT; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+#pragma unroll
+      for (int kk = 0; kk < LT_KEYS; kk += 16) {
+        uint32_t a[4];
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(ps + (lane & 15) * 72 + kk + (lane >> 4) * 8), a);
+#pragma unroll
+        for (int jp = 0; jp < LT_MAX_NT / 2; ++jp) {
+          if (2 * jp < ntw) {
+            uint32_t b[4];
+            ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(cs + (kk + (lane & 15)) * LDC + warp * (R / 4) + jp * 16 + (lane >> 4) * 8), b);
+            mma16816<T>(o[2 * jp], a, b[0], b[1]);
+            mma16816<T>(o[2 * jp + 1], a, b[2], b[3]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < LT_MAX_NT; ++i) {
+    if (i < ntw) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = (lane >> 2) + hf * 8;
+        if (r < nrow) {
+          const float inv = 1.f / row_l[r];
+          const int c = warp * (R / 4) + i * 8 + (lane & 3) * 2;
+          *reinterpret_cast<uint32_t*>(out + ((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R + c) =
+              pack2<T>(o[i][hf * 2] * inv, o[i][hf * 2 + 1] * inv);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace b200p
 
 using namespace b200p;
@@ -147,4 +297,38 @@ extern "C" int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap
     case B200P_BF16: return latent_attn_launch<__nv_bfloat16>(q, cache, Tcap, t_row, t_pos, out, M, H, R, window, scale, st);
     default: set_error("bad dtype %d", dtype); return B200P_ERR_ARG;
   }
+}
+
+template <typename T>
+static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
+                                   const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
+                                   cudaStream_t st) {
+  const size_t smem = ((size_t)(LT_KEYS + LT_ROWS) * (R + 8) + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
+  auto kern = latent_attn_tile_kernel<T>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(latent_attn_tile_kernel)");
+  }
+  const int by_head = max_n == 1 ? 1 : 0;       // one token per entry: tile over the heads instead of over the tokens
+  dim3 grid(by_head ? 1u : (unsigned)((max_n + LT_ROWS - 1) / LT_ROWS), by_head ? (unsigned)((H + LT_ROWS - 1) / LT_ROWS) : (unsigned)H,
+            (unsigned)nb);
+  kern<<<grid, LT_THREADS, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head);
+  B200P_LAUNCH_CHECK("latent_attn_tile_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_attn_tiles_supported(int R, int dtype) {
+  return (dtype == B200P_F16 || dtype == B200P_BF16) && R % 32 == 0 && R <= 32 * LT_MAX_NT ? 1 : 0;
+}
+
+extern "C" int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
+                                       const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window,
+                                       float scale, int dtype, void* stream) {
+  B200P_REQUIRE(q && cache && cu && rows && t_pos && out, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(b200p_latent_attn_tiles_supported(R, dtype), B200P_ERR_ARG, "the tile kernel needs a 16-bit type and a rank that is a multiple of 32, at most %d", 32 * LT_MAX_NT);
+  B200P_REQUIRE(nb > 0 && nb < 65536 && H > 0 && H < 65536 && max_n > 0, B200P_ERR_ARG, "bad batch geometry");
+  B200P_REQUIRE(aligned(cache, 16) && aligned(out, 4), B200P_ERR_ALIGN, "cache must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == B200P_F16) return latent_attn_tile_launch<__half>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
+  return latent_attn_tile_launch<__nv_bfloat16>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
 }

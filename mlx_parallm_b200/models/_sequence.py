@@ -158,7 +158,8 @@ class LatentAttention:
         ops.gemm(q, self.uk_t, GEMM_STORE_F32, out=qlat, batch=H, strides=(dk, R * dk, R), M=M, N=R, K=dk, ldx=H * dk, ldw=dk,
                  ldy=H * R)
         olat = s.get("olat", dt, M, H * R)
-        ops.latent_attn(qlat, cache.latent, plan["t_row"], plan["t_pos"], olat, H, R, self.window, self.scale)
+        ops.latent_attn(qlat, cache.latent, plan["t_row"], plan["t_pos"], olat, H, R, self.window, self.scale, cu=plan["cu"],
+                        rows=plan["rows"], nb=plan["nb"], max_n=plan["max_n"])
         mix = s.get("mix", dt, M, H * dv)
         ops.gemm(olat, self.uv, GEMM_STORE, out=mix, batch=H, strides=(R, dv * R, dv), M=M, N=dv, K=R, ldx=H * R, ldw=R, ldy=H * dv)
         return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
@@ -319,14 +320,16 @@ class SequenceModel:
         return a
 
     # -- forward ----------------------------------------------------------------------------------------------
-    def _layers_forward(self, ids_i32: torch.Tensor, B: int, L: int, cache: List[RowState], a: dict, M: Optional[int] = None):
+    def _layers_forward(self, ids_i32: torch.Tensor, B: int, L: int, cache: List[RowState], a: dict, M: Optional[int] = None,
+                        max_n: int = 1):
         """Run the packed tokens ``ids_i32`` ([M]) of the B entries described by a["cu"] / a["rows"] through every layer;
-        the residual stream is left in a["h"][:M].  (L is 1 for a decode step and unused otherwise: entries are ragged.)"""
+        the residual stream is left in a["h"][:M].  (L is 1 for a decode step and unused otherwise: entries are ragged;
+        ``max_n`` is the longest entry's token count, which picks prompt or decode kernels.)"""
         M = ids_i32.numel() if M is None else M
         s: Scratch = a["s"]
         dt, W = self.dtype, self.args.width
         lengths = cache[-1].lengths(self.device)
-        plan = dict(cu=a["cu"], rows=a["rows"], nb=B, lengths=lengths, t_row=a["t_row"][:M], t_pos=a["t_pos"][:M], t_off=a["t_off"][:M])
+        plan = dict(cu=a["cu"], rows=a["rows"], nb=B, lengths=lengths, max_n=max_n, t_row=a["t_row"][:M], t_pos=a["t_pos"][:M], t_off=a["t_off"][:M])
         ops.ragged_plan(a["cu"], a["rows"], lengths, plan["t_row"], plan["t_pos"], plan["t_off"], B, M)
         e = self.embed
         h = a["h"][:M]
@@ -404,7 +407,7 @@ class SequenceModel:
             ids.copy_(torch.tensor(flat, dtype=torch.int32), non_blocking=False)
             a["cu"].copy_(torch.tensor(cu, dtype=torch.int32))
             a["rows"].copy_(torch.tensor(rows, dtype=torch.int32))
-            self._layers_forward(ids, nb, 0, cache, a, M)
+            self._layers_forward(ids, nb, 0, cache, a, M, max_n=max(take))
             self._advance_device(cache, a, nb, ids)
             advance_rows(cache, rows, take)
             pick, where = [], []

@@ -356,10 +356,25 @@ def latent_prep(proj, q_rank, kv_rank, wq, wkv, eps, cq_out, cache, t_row, t_pos
                                                               _p(t_pos), M, dtype_code(cq_out.dtype), _stream()))
 
 
-def latent_attn(q, cache, t_row, t_pos, out, H, R, window, scale):
-    _dev(q, cache, t_row, t_pos, out)
+# The tensor-core tile kernel takes prompts (entries of at least LATENT_TILES_MIN_TOKENS tokens: tiles over tokens) and decode
+# steps of models with at least LATENT_TILES_MIN_HEADS heads (one token per entry: tiles over its heads); the per-token kernel
+# takes what is left (very short portions, few heads, float32, odd ranks).
+LATENT_TILES_MIN_TOKENS = 4
+LATENT_TILES_MIN_HEADS = 8
+
+
+def latent_attn(q, cache, t_row, t_pos, out, H, R, window, scale, cu=None, rows=None, nb=0, max_n=1):
+    """Windowed attention of H heads over the latent cache.  With the ragged description (cu, rows, nb, longest entry max_n)
+    prompts of 16-bit models run on the tensor-core tile kernel; everything else on the per-token kernel."""
+    _dev(q, cache, t_row, t_pos, out, cu, rows)
     M = q.shape[0]
     assert q.dtype == torch.float32 and q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and out.dtype == cache.dtype
+    if (cu is not None and (max_n >= LATENT_TILES_MIN_TOKENS or (max_n == 1 and H >= LATENT_TILES_MIN_HEADS))
+            and lib().b200p_latent_attn_tiles_supported(R, dtype_code(cache.dtype))):
+        _call("b200p_latent_attn_tiles", lambda: lib().b200p_latent_attn_tiles(_p(q), _p(cache), cache.shape[1], _p(cu), _p(rows),
+                                                                              _p(t_pos), _p(out), nb, int(max_n), H, R, int(window),
+                                                                              float(scale), dtype_code(cache.dtype), _stream()))
+        return out
     _call("b200p_latent_attn", lambda: lib().b200p_latent_attn(_p(q), _p(cache), cache.shape[1], _p(t_row), _p(t_pos), _p(out), M, H, R,
                                                               int(window), float(scale), dtype_code(cache.dtype), _stream()))
     return out
