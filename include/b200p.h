@@ -274,11 +274,18 @@ enum {
 };
 /* y = x . w^T, x [M,K] and w [N,K] in `dtype` (row strides ldx / ldw elements), fp32 accumulation; `batch` independent
  * products at element strides stride_x / stride_w / stride_y.  B200P_F32 runs true fp32 FMAs in ascending k.  16-bit calls
- * with K % 8 == 0 and 16-byte aligned rows take the tensor-core tile kernel (more than 8 rows) or the row-streaming kernel;
+ * with K % 8 == 0 and 16-byte aligned rows take the tensor-core tile kernels (more than 8 rows) or the row-streaming kernel;
  * everything else takes a generic kernel. */
 int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
                int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype, int epilogue, float limit,
                void* stream);
+
+/* 0 (default): calls of more than 64 rows run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators) and fall back
+ * to the mma.sync tile kernel for shapes it declines (K < 64); 1: mma.sync only. */
+int b200p_gemm_set_path(int path);
+/* 0, or 1 + the role (0 loader, 1 MMA issuer, 2 epilogue) whose bounded barrier wait ran out in a tcgen05 dense GEMM since the
+ * last call (which clears it).  Synchronises the device. */
+int b200p_gemm_tc_fault(void);
 
 /* t_row[t] = rows[e], t_pos[t] = lengths[rows[e]] + (t - cu[e]), t_off[t] = t - cu[e] for the entry e that owns token t */
 int b200p_ragged_plan(const int32_t* cu, const int32_t* rows, const int32_t* lengths, int32_t* t_row, int32_t* t_pos,

@@ -65,6 +65,8 @@ SIGNATURES = {
     "b200p_peer_status": (_i32, [_vp, _vp, _vp]),
     # dense linear layers, ragged batches, gated delta rule, latent attention
     "b200p_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
+    "b200p_gemm_set_path": (_i32, [_i32]),
+    "b200p_gemm_tc_fault": (_i32, []),
     "b200p_ragged_plan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp]),
     "b200p_ragged_advance": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _vp]),
     "b200p_embed_hashed": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i64, _i64, _i64, _i32, _vp]),
@@ -84,7 +86,7 @@ SIGNATURES = {
 # Translation units a model family needs (csrc/*.cu): the library can be linked from a subset, so that a fresh checkout
 # that serves one design compiles that design's kernels only.  ``None`` = every unit (libb200parallm.so).
 UNIT_SETS = {
-    "sequence": ("runtime", "dense_gemm", "ragged", "delta_rule", "latent_attn", "sampler"),
+    "sequence": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "latent_attn", "sampler"),
 }
 GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP = 0, 1, 2
 

@@ -1,14 +1,23 @@
 // Dense (unquantised) linear layers: y[M,N] = x[M,K] . w[N,K]^T with fp32 accumulation, optionally batched over a leading
-// index (one weight block per attention head).  Four kernels behind b200p_gemm:
-//   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles, two tile shapes      (more than 64 rows)
+// index (one weight block per attention head).  Five kernels behind b200p_gemm:
+//   gemm_tc_kernel     16-bit operands, tcgen05 / TMA / TMEM (dense_gemm_tc.cu)                             (more than 64 rows)
+//   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles, two tile shapes      (K < 64, or on request)
 //   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..64 rows: decode)
 //   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming                  (up to 8 rows)
 //   gemm_simt_kernel   any operand type and any shape or alignment; true fp32 FMA in ascending k for float32 models
 // Epilogues: store in the storage type, store fp32, and the clamped gated unit of b200p.h (gate / up rows interleaved).
+#include <type_traits>
+
 #include "common.cuh"
 #include "mma_util.cuh"
 
 namespace b200p {
+
+// dense_gemm_tc.cu: B200P_OK, an error, or 1 = "not a shape for the tcgen05 kernel"
+template <typename T>
+int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
+                   int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st);
+static int g_gemm_path = 0;   // 0: tcgen05 above 64 rows, mma.sync where it declines; 1: mma.sync only
 
 // ---- epilogue -------------------------------------------------------------------------------------------------------
 // value pair (even column n, odd column n+1) of one output row
@@ -341,7 +350,13 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
       B200P_LAUNCH_CHECK("gemm_stream_kernel");
       return B200P_OK;
     }
-    // 128 x 128 tiles once that grid covers most of the GPU's SMs, 64 x 64 below
+    if constexpr (!std::is_same<T, float>::value) {
+      if (g_gemm_path != 1) {
+        const int rc = gemm_tc_launch<T>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
+        if (rc != 1) return rc;
+      }
+    }
+    // mma.sync: 128 x 128 tiles once that grid covers most of the GPU's SMs, 64 x 64 below
     const int64_t big = ((M + 127) / 128) * ((N + 127) / 128) * batch;
     if (big >= 96) return gemm_mma_launch<T, 2, 2, 64, 64, 32, 4>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
     return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
@@ -353,6 +368,11 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
 }
 
 }  // namespace b200p
+
+extern "C" int b200p_gemm_set_path(int path) {
+  b200p::g_gemm_path = path == 1 ? 1 : 0;
+  return B200P_OK;
+}
 
 extern "C" int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
                           int64_t ldy, int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype,

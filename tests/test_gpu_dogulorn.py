@@ -101,6 +101,51 @@ def test_gemm_gated_epilogue_and_heads(dtype, M):
     assert (out.double().cpu() - want).abs().max() < 1e-4
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(65, 8, 64), (128, 72, 72), (300, 264, 200), (1000, 520, 512), (129, 1100, 64), (4100, 640, 136)])
+def test_gemm_tcgen05_tiles(dtype, M, N, K):
+    """More than 64 rows with K >= 64 run on tcgen05: ragged tile edges in all three dimensions, every tile width, all epilogues,
+    against float64 and against the mma.sync kernel."""
+    from mlx_parallm_b200 import _lib, ops
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) / 4).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / 4).to(dtype).cuda()
+    want = x.double() @ w.double().T
+    got = ops.gemm(x, w, _lib.GEMM_STORE_F32)
+    got16 = ops.gemm(x, w, _lib.GEMM_STORE)
+    L.b200p_gemm_set_path(1)
+    try:
+        other = ops.gemm(x, w, _lib.GEMM_STORE_F32)
+    finally:
+        L.b200p_gemm_set_path(0)
+    assert L.b200p_gemm_tc_fault() == 0
+    assert (got.double() - want).abs().max() <= 2e-5 * math.sqrt(K)
+    assert (got - other).abs().max() <= 2e-5 * math.sqrt(K)
+    assert got16.dtype == dtype and (got16.double() - want).abs().max() <= 0.02 * math.sqrt(K) / 4
+    if N % 2 == 0:
+        lim = 0.7
+        a = torch.clamp(want[:, 0::2], max=lim)
+        u = torch.clamp(want[:, 1::2], -lim, lim)
+        glu = ops.gemm(x, w, _lib.GEMM_GLU_CLAMP, limit=lim)
+        assert glu.shape == (M, N // 2) and (glu.double() - a * torch.sigmoid(1.702 * a) * (u + 1)).abs().max() < 0.02
+
+
+def test_gemm_tcgen05_heads_and_strides():
+    """One weight block per head, operands and outputs strided inside wider rows (3-d tensor maps)."""
+    from mlx_parallm_b200 import _lib, ops
+    g = torch.Generator().manual_seed(11)
+    M, H, dk, R = 330, 3, 64, 40
+    q = (torch.randn(M, H * dk, generator=g) / 4).to(torch.bfloat16).cuda()
+    wk = (torch.randn(H, R, dk, generator=g) / 4).to(torch.bfloat16).cuda()
+    want = torch.einsum("mhd,hrd->mhr", q.double().view(M, H, dk), wk.double()).reshape(M, H * R)
+    for epi, dt, tol in ((_lib.GEMM_STORE_F32, torch.float32, 2e-4), (_lib.GEMM_STORE, torch.bfloat16, 0.03)):
+        out = torch.full((M, H * R), 7.0, dtype=dt, device="cuda")
+        ops.gemm(q, wk, epi, out=out, batch=H, strides=(dk, R * dk, R), M=M, N=R, K=dk, ldx=H * dk, ldw=dk, ldy=H * R)
+        assert (out.double() - want).abs().max() < tol
+    assert _lib.lib().b200p_gemm_tc_fault() == 0
+
+
 def test_norm_add_norm_parts():
     from mlx_parallm_b200 import ops
     g = torch.Generator().manual_seed(1)
