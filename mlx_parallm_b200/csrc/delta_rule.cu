@@ -2,7 +2,7 @@
 // current value along the current key and read with the current query), as four kernels over a ragged batch:
 //   delta_prep_kernel         short causal convolution + silu of q, k, v; unit q / k per head; beta and decay   (per token)
 //   delta_conv_commit_kernel  the convolution's carried inputs                                                   (per entry)
-//   delta_scan_kernel         the recurrence, one thread per state column, fp32, token by token                   (per entry, head)
+//   delta_scan_kernel         the recurrence, four lanes per state column, fp32, token by token                   (per entry, head)
 //   delta_out_kernel          per-head rms norm * weight * silu(gate)                                            (per token)
 // Prompts and single decoded tokens run the SAME scan kernel in the same summation order, so a prompt cut into portions gives
 // the same numbers as one pass.
@@ -79,35 +79,45 @@ __global__ void delta_conv_commit_kernel(const float* __restrict__ proj, int64_t
     if (i < taps - 1) st[(int64_t)i * C] = keep[i];
 }
 
-constexpr int DS_CHUNK = 8;       // tokens whose q, k, v, beta, decay are staged in shared memory at a time
-constexpr int DS_THREADS = 128;   // state columns per CTA (threads past dv only help with the staging)
+constexpr int DS_THREADS = 128;   // 32 state columns x 4 lanes per CTA
+constexpr int DS_LANES = 4;       // lanes that share one state column: lane l keeps rows [l * dkp / 4, (l + 1) * dkp / 4) in registers
+constexpr int DS_COLS = DS_THREADS / DS_LANES;
 
-template <int DKP>                // dk padded to 32 / 64 / 128 / 256: one state column per thread, in registers
+// dk padded to DKP = 32 ... 512.  A state column is spread over four neighbouring lanes (a quarter of its rows each), so a head's
+// value size of 128 gives 512 threads per (sequence, head) instead of 128 and the two reductions over dk are a quarter as long
+// plus two shuffles.  q and k of CHUNK tokens are staged in shared memory with every quarter padded by 16 bytes: the four
+// lanes' 128-bit reads then fall into different banks.
+template <int DKP>
 __global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ lengths,
                   float* __restrict__ o, int H, int KH, int dk, int dv) {
-  constexpr int PF = DS_CHUNK * DKP / DS_THREADS;                // q / k elements each thread stages per chunk
-  __shared__ __align__(16) float ks[2][DS_CHUNK][DKP], qs[2][DS_CHUNK][DKP];
-  __shared__ float vs[2][DS_CHUNK][DS_THREADS], gs[2][DS_CHUNK], bs[2][DS_CHUNK];
+  constexpr int SEG = DKP / DS_LANES;                            // state rows per lane
+  constexpr int CHUNK = DKP <= 128 ? 8 : 1024 / DKP;             // tokens staged at a time
+  constexpr int LDK = DKP + 4 * DS_LANES;                        // padded row of the staging buffers
+  constexpr int PF = CHUNK * DKP / DS_THREADS;                   // q / k elements each thread stages per chunk
+  constexpr int PV = (CHUNK * DS_COLS + DS_THREADS - 1) / DS_THREADS;
+  __shared__ __align__(16) float ks[2][CHUNK][LDK], qs[2][CHUNK][LDK];
+  __shared__ float vs[2][CHUNK][DS_COLS], gs[2][CHUNK], bs[2][CHUNK];
   const int e = blockIdx.x, h = blockIdx.y;
-  const int j = blockIdx.z * DS_THREADS + threadIdx.x;           // state column
+  const int l = threadIdx.x & (DS_LANES - 1), col = threadIdx.x / DS_LANES;
+  const int j = blockIdx.z * DS_COLS + col;                      // state column
   const bool live = j < dv;
   const int t0 = cu[e], t1 = cu[e + 1];
   if (t1 <= t0) return;
   const int row = rows[e];
   const int kh = h / (H / KH);
-  float S[DKP];
-  float* sp = state + (((int64_t)row * H + h) * dk) * dv + j;
+  float S[SEG];
+  float* sp = state + (((int64_t)row * H + h) * dk + l * SEG) * dv + j;
   const bool fresh = lengths[row] == 0;                          // first token of a sequence: the state starts at zero
 #pragma unroll
-  for (int i = 0; i < DKP; ++i) S[i] = (!fresh && live && i < dk) ? sp[(int64_t)i * dv] : 0.f;
+  for (int i = 0; i < SEG; ++i) S[i] = (!fresh && live && l * SEG + i < dk) ? sp[(int64_t)i * dv] : 0.f;
   // The next chunk's inputs are fetched into registers while the current chunk runs out of shared memory, then parked in the
   // other buffer: the recurrence never waits for global memory.
-  float pk[PF], pq[PF], pv[DS_CHUNK], pg = 0.f, pb = 0.f;
+  float pk[PF], pq[PF], pv[PV], pg = 0.f, pb = 0.f;
   auto fetch = [&](int tc) {
-    const int nt = min(DS_CHUNK, t1 - tc);
+    const int nt = min(CHUNK, t1 - tc);
 #pragma unroll
     for (int r = 0; r < PF; ++r) {
       const int idx = threadIdx.x + r * DS_THREADS, tt = idx / DKP, i = idx % DKP;
@@ -117,7 +127,10 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       pq[r] = ok ? qn[src] : 0.f;
     }
 #pragma unroll
-    for (int tt = 0; tt < DS_CHUNK; ++tt) pv[tt] = (live && tt < nt) ? v[((int64_t)(tc + tt) * H + h) * dv + j] : 0.f;
+    for (int r = 0; r < PV; ++r) {
+      const int idx = threadIdx.x + r * DS_THREADS, tt = idx / DS_COLS, c = blockIdx.z * DS_COLS + idx % DS_COLS;
+      pv[r] = (tt < nt && c < dv) ? v[((int64_t)(tc + tt) * H + h) * dv + c] : 0.f;
+    }
     if (threadIdx.x < nt) {
       pg = decay[(int64_t)(tc + threadIdx.x) * H + h];
       pb = beta[(int64_t)(tc + threadIdx.x) * H + h];
@@ -126,55 +139,66 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   auto park = [&](int buf) {
 #pragma unroll
     for (int r = 0; r < PF; ++r) {
-      const int idx = threadIdx.x + r * DS_THREADS;
-      ks[buf][idx / DKP][idx % DKP] = pk[r];
-      qs[buf][idx / DKP][idx % DKP] = pq[r];
+      const int idx = threadIdx.x + r * DS_THREADS, tt = idx / DKP, i = idx % DKP;
+      ks[buf][tt][i + (i / SEG) * 4] = pk[r];
+      qs[buf][tt][i + (i / SEG) * 4] = pq[r];
     }
 #pragma unroll
-    for (int tt = 0; tt < DS_CHUNK; ++tt) vs[buf][tt][threadIdx.x] = pv[tt];
-    if (threadIdx.x < DS_CHUNK) { gs[buf][threadIdx.x] = pg; bs[buf][threadIdx.x] = pb; }
+    for (int r = 0; r < PV; ++r) {
+      const int idx = threadIdx.x + r * DS_THREADS;
+      if (idx < CHUNK * DS_COLS) vs[buf][idx / DS_COLS][idx % DS_COLS] = pv[r];
+    }
+    if (threadIdx.x < CHUNK) { gs[buf][threadIdx.x] = pg; bs[buf][threadIdx.x] = pb; }
   };
   fetch(t0);
   park(0);
   __syncthreads();
   int buf = 0;
-  for (int tc = t0; tc < t1; tc += DS_CHUNK, buf ^= 1) {
-    const int nt = min(DS_CHUNK, t1 - tc);
-    const bool more = tc + DS_CHUNK < t1;
-    if (more) fetch(tc + DS_CHUNK);
+  for (int tc = t0; tc < t1; tc += CHUNK, buf ^= 1) {
+    const int nt = min(CHUNK, t1 - tc);
+    const bool more = tc + CHUNK < t1;
+    if (more) fetch(tc + CHUNK);
     for (int tt = 0; tt < nt; ++tt) {
-      const float vj = vs[buf][tt][threadIdx.x];
+      const float vj = vs[buf][tt][col];
       const float g = gs[buf][tt];
-      // both reductions run as four interleaved partial sums (i mod 4), always combined in the same order: four times shorter
-      // dependency chains, and the same numbers whether a token arrives in a prompt or alone
+      const float* kp = &ks[buf][tt][l * (SEG + 4)];
+      const float* qp = &qs[buf][tt][l * (SEG + 4)];
+      // both reductions run as four interleaved partial sums per lane, combined in a fixed order and then across the four lanes
+      // by two exchanges: short dependency chains, and the same numbers whether a token arrives in a prompt or alone
       float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DKP; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[buf][tt][i]);
+      for (int i = 0; i < SEG; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
         S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
         d4[0] = fmaf(S[i], k4.x, d4[0]); d4[1] = fmaf(S[i + 1], k4.y, d4[1]);
         d4[2] = fmaf(S[i + 2], k4.z, d4[2]); d4[3] = fmaf(S[i + 3], k4.w, d4[3]);
       }
-      const float u = bs[buf][tt] * (vj - ((d4[0] + d4[1]) + (d4[2] + d4[3])));
+      float d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      const float u = bs[buf][tt] * (vj - d);
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DKP; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[buf][tt][i]);
-        const float4 q4 = *reinterpret_cast<const float4*>(&qs[buf][tt][i]);
+      for (int i = 0; i < SEG; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
         S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
         S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
         o4[0] = fmaf(S[i], q4.x, o4[0]); o4[1] = fmaf(S[i + 1], q4.y, o4[1]);
         o4[2] = fmaf(S[i + 2], q4.z, o4[2]); o4[3] = fmaf(S[i + 3], q4.w, o4[3]);
       }
-      if (live) o[((int64_t)(tc + tt) * H + h) * dv + j] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      float ov = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      ov += __shfl_xor_sync(0xffffffffu, ov, 1);
+      ov += __shfl_xor_sync(0xffffffffu, ov, 2);
+      if (live && l == 0) o[((int64_t)(tc + tt) * H + h) * dv + j] = ov;
     }
     if (more) park(buf ^ 1);          // the other buffer was last read in the previous iteration, before its closing barrier
     __syncthreads();
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DKP; ++i)
-      if (i < dk) sp[(int64_t)i * dv] = S[i];
+    for (int i = 0; i < SEG; ++i)
+      if (l * SEG + i < dk) sp[(int64_t)i * dv] = S[i];
   }
 }
 
@@ -232,14 +256,15 @@ extern "C" int b200p_delta_scan(const float* qn, const float* kn, const float* v
                                 int H, int KH, int dk, int dv, void* stream) {
   B200P_REQUIRE(qn && kn && v && beta && decay && state && cu && rows && lengths && o, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(nb > 0 && H > 0 && KH > 0 && H % KH == 0 && H < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
-  B200P_REQUIRE(dk <= 256, B200P_ERR_ARG, "key size %d > 256 is not built", dk);
+  B200P_REQUIRE(dk <= 512, B200P_ERR_ARG, "key size %d > 512 is not built", dk);
   const int threads = DS_THREADS;
-  dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + threads - 1) / threads));
+  dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + DS_COLS - 1) / DS_COLS));
   cudaStream_t st = (cudaStream_t)stream;
   if (dk <= 32) delta_scan_kernel<32><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
   else if (dk <= 64) delta_scan_kernel<64><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
   else if (dk <= 128) delta_scan_kernel<128><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
-  else delta_scan_kernel<256><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 256) delta_scan_kernel<256><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else delta_scan_kernel<512><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
   B200P_LAUNCH_CHECK("delta_scan_kernel");
   return B200P_OK;
 }
