@@ -280,8 +280,8 @@ int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int6
                int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype, int epilogue, float limit,
                void* stream);
 
-/* 0 (default): calls of more than 64 rows run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators) and fall back
- * to the mma.sync tile kernel for shapes it declines (K < 64); 1: mma.sync only. */
+/* 0 (default): calls of more than 16 rows run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators) and fall back
+ * to the mma.sync kernels for shapes it declines (K < 64); 1: mma.sync kernels only; 2: tcgen05 from 9 rows. */
 int b200p_gemm_set_path(int path);
 /* 0, or 1 + the role (0 loader, 1 MMA issuer, 2 epilogue) whose bounded barrier wait ran out in a tcgen05 dense GEMM since the
  * last call (which clears it).  Synchronises the device. */

@@ -1,8 +1,8 @@
 // Dense (unquantised) linear layers: y[M,N] = x[M,K] . w[N,K]^T with fp32 accumulation, optionally batched over a leading
 // index (one weight block per attention head).  Five kernels behind b200p_gemm:
-//   gemm_tc_kernel     16-bit operands, tcgen05 / TMA / TMEM (dense_gemm_tc.cu)                             (more than 64 rows)
+//   gemm_tc_kernel     16-bit operands, tcgen05 / TMA / TMEM (dense_gemm_tc.cu)                             (more than 16 rows)
 //   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles, two tile shapes      (K < 64, or on request)
-//   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..64 rows: decode)
+//   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..16 rows: decode)
 //   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming                  (up to 8 rows)
 //   gemm_simt_kernel   any operand type and any shape or alignment; true fp32 FMA in ascending k for float32 models
 // Epilogues: store in the storage type, store fp32, and the clamped gated unit of b200p.h (gate / up rows interleaved).
@@ -17,7 +17,9 @@ namespace b200p {
 template <typename T>
 int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
                    int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st);
-static int g_gemm_path = 0;   // 0: tcgen05 above 64 rows, mma.sync where it declines; 1: mma.sync only
+// 0: tcgen05 above 16 rows (at 32 rows it already streams the weights 1.2-1.5x faster than gemm_stream_kernel, at 64 rows 2-3x),
+//    the mma.sync kernels where it declines; 1: mma.sync kernels only; 2: tcgen05 from 9 rows
+static int g_gemm_path = 0;
 
 // ---- epilogue -------------------------------------------------------------------------------------------------------
 // value pair (even column n, odd column n+1) of one output row
@@ -342,6 +344,12 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
     return B200P_OK;
   }
   if (fast_ok) {
+    if constexpr (!std::is_same<T, float>::value) {
+      if (M <= 64 && g_gemm_path != 1 && (M > 16 || g_gemm_path == 2)) {
+        const int rc = gemm_tc_launch<T>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
+        if (rc != 1) return rc;
+      }
+    }
     if (M <= 64) {
       dim3 grid((unsigned)((N + 15) / 16), 1, (unsigned)batch);
       if (M <= 16) gemm_stream_kernel<T, 1><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
@@ -370,7 +378,7 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
 }  // namespace b200p
 
 extern "C" int b200p_gemm_set_path(int path) {
-  b200p::g_gemm_path = path == 1 ? 1 : 0;
+  b200p::g_gemm_path = (path == 1 || path == 2) ? path : 0;
   return B200P_OK;
 }
 

@@ -102,7 +102,7 @@ def test_gemm_gated_epilogue_and_heads(dtype, M):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,N,K", [(65, 8, 64), (128, 72, 72), (300, 264, 200), (1000, 520, 512), (129, 1100, 64), (4100, 640, 136)])
+@pytest.mark.parametrize("M,N,K", [(17, 72, 64), (40, 264, 200), (64, 520, 128), (65, 8, 64), (128, 72, 72), (300, 264, 200), (1000, 520, 512), (129, 1100, 64), (4100, 640, 136)])
 def test_gemm_tcgen05_tiles(dtype, M, N, K):
     """More than 64 rows with K >= 64 run on tcgen05: ragged tile edges in all three dimensions, every tile width, all epilogues,
     against float64 and against the mma.sync kernel."""
