@@ -341,7 +341,7 @@ int b200p_latent_prep(const float* proj, int64_t ldp, int q_rank, int kv_rank, c
                       void* stream);
 /* step 2: H heads attend over the ONE latent per position (keys and values both): q fp32 [M, H, R] are the queries already
  * carried into the latent space; token t at position p sees positions j with 0 <= p - j < window (window <= 0: all j <= p);
- * fp32 softmax of q . c_j * scale; out [M, H, R] (dtype) = sum_j p_j c_j.  R <= 512. */
+ * fp32 softmax of q . c_j * scale; out [M, H, R] (dtype) = sum_j p_j c_j.  R <= 1024. */
 int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, void* out,
                       int64_t M, int H, int R, int64_t window, float scale, int dtype, void* stream);
 /* The same attention on the tensor cores: tiles of 16 consecutive tokens of one entry and one head (max_n = the longest
@@ -349,6 +349,9 @@ int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap, const int
  * R % 32 == 0, R <= 512 (b200p_latent_attn_tiles_supported says whether a call
  * qualifies).  q and p are rounded to the storage type for the products; max, sum and the accumulators are fp32. */
 int b200p_latent_attn_tiles_supported(int R, int dtype);
+/* 16-row tiles (heads of a prompt tile, or blocks of 16 heads of a decode step) that one CTA of the tile kernel serves from one
+ * staged copy of the keys: 1..4, or 0 for the built-in choice. */
+int b200p_latent_attn_set_groups(int groups);
 int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                             const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                             int dtype, void* stream);

@@ -2,7 +2,7 @@
 // current value along the current key and read with the current query), as four kernels over a ragged batch:
 //   delta_prep_kernel         short causal convolution + silu of q, k, v; unit q / k per head; beta and decay   (per token)
 //   delta_conv_commit_kernel  the convolution's carried inputs                                                   (per entry)
-//   delta_scan_kernel         the recurrence, four lanes per state column, fp32, token by token                   (per entry, head)
+//   delta_scan_kernel         the recurrence, fp32, token by token; four lanes per pair of state columns           (per entry, head)
 //   delta_out_kernel          per-head rms norm * weight * silu(gate)                                            (per token)
 // Prompts and single decoded tokens run the SAME scan kernel in the same summation order, so a prompt cut into portions gives
 // the same numbers as one pass.
@@ -79,20 +79,24 @@ __global__ void delta_conv_commit_kernel(const float* __restrict__ proj, int64_t
     if (i < taps - 1) st[(int64_t)i * C] = keep[i];
 }
 
-constexpr int DS_THREADS = 128;   // 32 state columns x 4 lanes per CTA
-constexpr int DS_LANES = 4;       // lanes that share one state column: lane l keeps rows [l * dkp / 4, (l + 1) * dkp / 4) in registers
-constexpr int DS_COLS = DS_THREADS / DS_LANES;
+constexpr int DS_THREADS = 128;
+// lanes that share a state column (lane l keeps rows [l * dkp / lanes, (l + 1) * dkp / lanes) in registers): at most 32 rows each
+constexpr int ds_lanes(int dkp) { return dkp <= 128 ? 4 : dkp / 32; }
+constexpr int ds_cols(int dkp) { return 2 * DS_THREADS / ds_lanes(dkp); }      // state columns per CTA: two per column slot
 
-// dk padded to DKP = 32 ... 512.  A state column is spread over four neighbouring lanes (a quarter of its rows each), so a head's
-// value size of 128 gives 512 threads per (sequence, head) instead of 128 and the two reductions over dk are a quarter as long
-// plus two shuffles.  q and k of CHUNK tokens are staged in shared memory with every quarter padded by 16 bytes: the four
-// lanes' 128-bit reads then fall into different banks.
+// dk padded to DKP = 32 ... 512.  A thread owns a part (a quarter up to 128 rows, 32 rows beyond) of the rows of TWO state
+// columns, kept as float2 pairs: a head's value size of 128 is spread over 256 threads instead of 128, every q / k element read
+// from shared memory serves two columns (shared-memory wavefronts, not arithmetic, bound the one-column variants), and the
+// packed fp32 instructions of sm_100 (FMUL2 / FFMA2: both halves rounded like the scalar operation) update both columns at
+// once.  Each reduction over dk is as much shorter plus log2(lanes) exchanges between the lanes.  q and k of CHUNK tokens are
+// staged in shared memory with every lane's part padded by 16 bytes, so the lanes' 128-bit reads fall into different banks.
 template <int DKP>
 __global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ lengths,
                   float* __restrict__ o, int H, int KH, int dk, int dv) {
+  constexpr int DS_LANES = ds_lanes(DKP), DS_SLOTS = DS_THREADS / DS_LANES, DS_COLS = 2 * DS_SLOTS;
   constexpr int SEG = DKP / DS_LANES;                            // state rows per lane
   constexpr int CHUNK = DKP <= 128 ? 8 : 1024 / DKP;             // tokens staged at a time
   constexpr int LDK = DKP + 4 * DS_LANES;                        // padded row of the staging buffers
@@ -101,18 +105,22 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   __shared__ __align__(16) float ks[2][CHUNK][LDK], qs[2][CHUNK][LDK];
   __shared__ float vs[2][CHUNK][DS_COLS], gs[2][CHUNK], bs[2][CHUNK];
   const int e = blockIdx.x, h = blockIdx.y;
-  const int l = threadIdx.x & (DS_LANES - 1), col = threadIdx.x / DS_LANES;
-  const int j = blockIdx.z * DS_COLS + col;                      // state column
-  const bool live = j < dv;
+  const int l = threadIdx.x & (DS_LANES - 1), slot = threadIdx.x / DS_LANES;
+  const int j0 = blockIdx.z * DS_COLS + slot, j1 = j0 + DS_SLOTS;                // this thread's two state columns
+  const bool live0 = j0 < dv, live1 = j1 < dv;
   const int t0 = cu[e], t1 = cu[e + 1];
   if (t1 <= t0) return;
   const int row = rows[e];
   const int kh = h / (H / KH);
-  float S[SEG];
-  float* sp = state + (((int64_t)row * H + h) * dk + l * SEG) * dv + j;
+  float2 S2[SEG];                                                // .x: column j0, .y: column j1
+  float* sp = state + (((int64_t)row * H + h) * dk + l * SEG) * dv;
   const bool fresh = lengths[row] == 0;                          // first token of a sequence: the state starts at zero
 #pragma unroll
-  for (int i = 0; i < SEG; ++i) S[i] = (!fresh && live && l * SEG + i < dk) ? sp[(int64_t)i * dv] : 0.f;
+  for (int i = 0; i < SEG; ++i) {
+    const bool in = !fresh && l * SEG + i < dk;
+    S2[i].x = (in && live0) ? sp[(int64_t)i * dv + j0] : 0.f;
+    S2[i].y = (in && live1) ? sp[(int64_t)i * dv + j1] : 0.f;
+  }
   // The next chunk's inputs are fetched into registers while the current chunk runs out of shared memory, then parked in the
   // other buffer: the recurrence never waits for global memory.
   float pk[PF], pq[PF], pv[PV], pg = 0.f, pb = 0.f;
@@ -159,46 +167,70 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     const bool more = tc + CHUNK < t1;
     if (more) fetch(tc + CHUNK);
     for (int tt = 0; tt < nt; ++tt) {
-      const float vj = vs[buf][tt][col];
-      const float g = gs[buf][tt];
+      const float2 v2 = make_float2(vs[buf][tt][slot], vs[buf][tt][slot + DS_SLOTS]);
+      const float g = gs[buf][tt], b = bs[buf][tt];
+      const float2 g2 = make_float2(g, g);
       const float* kp = &ks[buf][tt][l * (SEG + 4)];
       const float* qp = &qs[buf][tt][l * (SEG + 4)];
-      // both reductions run as four interleaved partial sums per lane, combined in a fixed order and then across the four lanes
-      // by two exchanges: short dependency chains, and the same numbers whether a token arrives in a prompt or alone
-      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+      // both reductions run as four interleaved partial sums per lane (rows i mod 4), combined in a fixed order and then across
+      // the lanes by exchanges: short dependency chains, and the same numbers whether a token arrives in a prompt or
+      // alone
+      float2 d[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) d[a] = make_float2(0.f, 0.f);
+      float4 kr[SEG / 4];                                        // the keys stay in registers for the update below
 #pragma unroll
       for (int i = 0; i < SEG; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
-        S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-        d4[0] = fmaf(S[i], k4.x, d4[0]); d4[1] = fmaf(S[i + 1], k4.y, d4[1]);
-        d4[2] = fmaf(S[i + 2], k4.z, d4[2]); d4[3] = fmaf(S[i + 3], k4.w, d4[3]);
+        const float4 k4 = kr[i / 4] = *reinterpret_cast<const float4*>(kp + i);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          S2[i + a] = __fmul2_rn(S2[i + a], g2);
+          d[a] = __ffma2_rn(S2[i + a], make_float2(kk[a], kk[a]), d[a]);
+        }
       }
-      float d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-      d += __shfl_xor_sync(0xffffffffu, d, 1);
-      d += __shfl_xor_sync(0xffffffffu, d, 2);
-      const float u = bs[buf][tt] * (vj - d);
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+      float dx = (d[0].x + d[1].x) + (d[2].x + d[3].x), dy = (d[0].y + d[1].y) + (d[2].y + d[3].y);
+#pragma unroll
+      for (int m = 1; m < DS_LANES; m <<= 1) {
+        dx += __shfl_xor_sync(0xffffffffu, dx, m);
+        dy += __shfl_xor_sync(0xffffffffu, dy, m);
+      }
+      const float2 u2 = make_float2(b * (v2.x - dx), b * (v2.y - dy));
+      float2 oa[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) oa[a] = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < SEG; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
+        const float4 k4 = kr[i / 4];
         const float4 q4 = *reinterpret_cast<const float4*>(qp + i);
-        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
-        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
-        o4[0] = fmaf(S[i], q4.x, o4[0]); o4[1] = fmaf(S[i + 1], q4.y, o4[1]);
-        o4[2] = fmaf(S[i + 2], q4.z, o4[2]); o4[3] = fmaf(S[i + 3], q4.w, o4[3]);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          S2[i + a] = __ffma2_rn(make_float2(kk[a], kk[a]), u2, S2[i + a]);
+          oa[a] = __ffma2_rn(S2[i + a], make_float2(qq[a], qq[a]), oa[a]);
+        }
       }
-      float ov = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-      ov += __shfl_xor_sync(0xffffffffu, ov, 1);
-      ov += __shfl_xor_sync(0xffffffffu, ov, 2);
-      if (live && l == 0) o[((int64_t)(tc + tt) * H + h) * dv + j] = ov;
+      float ox = (oa[0].x + oa[1].x) + (oa[2].x + oa[3].x), oy = (oa[0].y + oa[1].y) + (oa[2].y + oa[3].y);
+#pragma unroll
+      for (int m = 1; m < DS_LANES; m <<= 1) {
+        ox += __shfl_xor_sync(0xffffffffu, ox, m);
+        oy += __shfl_xor_sync(0xffffffffu, oy, m);
+      }
+      if (l == 0) {
+        float* op = o + ((int64_t)(tc + tt) * H + h) * dv;
+        if (live0) op[j0] = ox;
+        if (live1) op[j1] = oy;
+      }
     }
     if (more) park(buf ^ 1);          // the other buffer was last read in the previous iteration, before its closing barrier
     __syncthreads();
   }
-  if (live) {
 #pragma unroll
-    for (int i = 0; i < SEG; ++i)
-      if (l * SEG + i < dk) sp[(int64_t)i * dv] = S[i];
+  for (int i = 0; i < SEG; ++i) {
+    if (l * SEG + i < dk) {
+      if (live0) sp[(int64_t)i * dv + j0] = S2[i].x;
+      if (live1) sp[(int64_t)i * dv + j1] = S2[i].y;
+    }
   }
 }
 
@@ -258,7 +290,8 @@ extern "C" int b200p_delta_scan(const float* qn, const float* kn, const float* v
   B200P_REQUIRE(nb > 0 && H > 0 && KH > 0 && H % KH == 0 && H < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dk <= 512, B200P_ERR_ARG, "key size %d > 512 is not built", dk);
   const int threads = DS_THREADS;
-  dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + DS_COLS - 1) / DS_COLS));
+  const int dkp = dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : dk <= 256 ? 256 : 512, cols = ds_cols(dkp);
+  dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + cols - 1) / cols));
   cudaStream_t st = (cudaStream_t)stream;
   if (dk <= 32) delta_scan_kernel<32><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
   else if (dk <= 64) delta_scan_kernel<64><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);

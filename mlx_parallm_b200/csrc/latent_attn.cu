@@ -4,9 +4,9 @@
 //   latent_prep_kernel   rms norms of the two down-projections; the key/value latent goes into the cache
 //   latent_attn_kernel   one CTA per token and group of heads; keys staged 32 at a time in shared memory; online fp32 softmax
 //                        (decode steps, float32 models, ranks off the tensor-core shapes)
-//   latent_attn_tile_kernel  16-bit models: a tile of 16 query rows per CTA (prompts: 16 consecutive tokens of one sequence for
-//                        one head; decode steps: 16 heads of the one new token, which all read the same keys), mma.sync
-//                        m16n8k16 for q.c and p.c over 64-key chunks staged once for both products
+//   latent_attn_tile_kernel  16-bit models: up to four tiles of 16 query rows per CTA (prompts: 16 consecutive tokens of one
+//                        sequence for one head each; decode steps: 16 heads each of the one new token), mma.sync m16n8k16 for
+//                        q.c and p.c over 64-key chunks staged once for both products and for all the CTA's tiles
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -41,7 +41,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int64_t ldp, 
 
 constexpr int LA_KEYS = 32;       // keys per staged chunk: one per lane in the score phase
 constexpr int LA_MAX_HEADS = 8;   // heads (warps) per CTA
-constexpr int LA_MAX_RL = 16;     // latent elements per lane in the output phase: R <= 512
+constexpr int LA_MAX_RL = 32;     // latent elements per lane in the output phase: R <= 1024
 
 template <typename T>
 __global__ void __launch_bounds__(LA_MAX_HEADS * 32)
@@ -110,45 +110,50 @@ latent_attn_kernel(const float* __restrict__ q, const T* __restrict__ cache, int
 
 
 // ---- prompts on the tensor cores -----------------------------------------------------------------------------------------
-// CTA = (tile of 16 tokens of entry e, head h), 4 warps.  Per chunk of 64 positions of the latent cache (staged by cp.async,
-// one copy serves keys and values):
+// CTA = (tile of 16 tokens of entry e, G heads), G groups of 4 warps; group g owns one head.  All heads read the same latent
+// cache, so a chunk of 64 positions is staged ONCE per CTA (cp.async; one copy serves keys and values of all G heads): the
+// L2 -> shared traffic per head falls by G, which is what bounded the one-head tile.  Per chunk, in every group:
 //   S   warp w: scores of its 16 keys, q [16, R] x c[16 keys, R]^T                     -> shared S [16, 64] fp32, masked
 //   P   8 threads per row: running max / sum in fp32, p = exp(s - max) as 16-bit       -> shared P [16, 64]
 //   O   warp w: columns [w R/4, (w+1) R/4) of o [16, R] += P x c[64 keys, its columns]   (accumulators rescaled first)
 constexpr int LT_ROWS = 16, LT_KEYS = 64, LT_THREADS = 128, LT_MAX_NT = 16;      // R <= 512, R % 32 == 0
+constexpr int LT_MAX_GROUPS = 4;
 
-template <typename T>
-__global__ void __launch_bounds__(LT_THREADS)
+template <typename T, int G>
+__global__ void __launch_bounds__(LT_THREADS * G)
 latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache, int64_t Tcap, const int32_t* __restrict__ cu,
                         const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos, T* __restrict__ out, int H, int R,
                         int64_t window, float scale, int by_head) {
   extern __shared__ __align__(128) uint8_t lt_smem[];
-  // by_head == 0: rows of the tile are 16 consecutive tokens of entry e = blockIdx.z, for head blockIdx.y (prompts)
+  // by_head == 0: rows of a group's tile are 16 consecutive tokens of entry e = blockIdx.z, for ONE head (prompts)
   // by_head == 1: rows are 16 consecutive heads of the ONE token of entry e (decode: every head reads the same keys)
   const int e = blockIdx.z;
-  const int h = by_head ? blockIdx.y * LT_ROWS : blockIdx.y;
+  const int grp = threadIdx.x / LT_THREADS, tl = threadIdx.x % LT_THREADS;
+  const int h = by_head ? (blockIdx.y * G + grp) * LT_ROWS : blockIdx.y * G + grp;
   const int t0 = by_head ? cu[e] : cu[e] + blockIdx.x * LT_ROWS;
-  const int nrow = by_head ? (cu[e + 1] > cu[e] ? min(LT_ROWS, H - h) : 0) : min(LT_ROWS, cu[e + 1] - t0);    // live rows
-  if (nrow <= 0) return;
+  if ((by_head ? cu[e + 1] - cu[e] : cu[e + 1] - t0) <= 0) return;             // the same for every thread of the CTA
+  const bool active = h < H;                                     // a group past the last head only helps to stage the chunks
+  const int nrow = !active ? 0 : by_head ? min(LT_ROWS, H - h) : min(LT_ROWS, cu[e + 1] - t0);               // live rows
   const int tstep = by_head ? 0 : 1, hstep = by_head ? 1 : 0;   // row r is token t0 + r * tstep, head h + r * hstep
   const int LDC = R + 8;                                         // padded rows: ldmatrix reads 8 rows without bank conflicts
-  T* cs = reinterpret_cast<T*>(lt_smem);                         // [64][LDC]
-  T* qs = cs + LT_KEYS * LDC;                                    // [16][LDC]
+  T* cs = reinterpret_cast<T*>(lt_smem);                         // [64][LDC], shared by the groups
+  const size_t group_bytes = (size_t)(LT_ROWS * LDC + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
+  T* qs = reinterpret_cast<T*>(lt_smem + (size_t)LT_KEYS * LDC * sizeof(T) + grp * group_bytes);             // [16][LDC]
   T* ps = qs + LT_ROWS * LDC;                                    // [16][72]
   float* ss = reinterpret_cast<float*>(ps + LT_ROWS * 72);       // [16][68]
   float* row_m = ss + LT_ROWS * 68;                              // running max, sum, and this chunk's rescale factor
   float* row_l = row_m + LT_ROWS;
   float* row_c = row_l + LT_ROWS;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = tl >> 5, lane = tl & 31;                     // warp inside the group
   const int64_t p0 = t_pos[t0];                                  // positions of the tile's rows are p0, p0 + 1, ...
-  const int64_t plast = by_head ? p0 : p0 + nrow - 1;
+  const int64_t plast = by_head ? p0 : p0 + min(LT_ROWS, cu[e + 1] - t0) - 1;
   const int64_t kmin = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const T* cbase = cache + (int64_t)rows[e] * Tcap * R;
-  for (int idx = threadIdx.x; idx < LT_ROWS * R; idx += LT_THREADS) {
+  for (int idx = tl; idx < LT_ROWS * R; idx += LT_THREADS) {
     const int r = idx / R, c = idx % R;
     qs[r * LDC + c] = Tr<T>::from_f(r < nrow ? q[((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R + c] : 0.f);
   }
-  if (threadIdx.x < LT_ROWS) { row_m[threadIdx.x] = -INFINITY; row_l[threadIdx.x] = 0.f; }
+  if (tl < LT_ROWS) { row_m[tl] = -INFINITY; row_l[tl] = 0.f; }
   const int ntw = R / 32;                                        // 8-column tiles of o per warp
   float o[LT_MAX_NT][4];
 #pragma unroll
@@ -156,7 +161,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
   const int chunks_per_row = R / 8;
   for (int64_t j0 = kmin; j0 <= plast; j0 += LT_KEYS) {
     __syncthreads();                                             // the previous chunk's products are done with cs / ss / ps
-    for (int idx = threadIdx.x; idx < LT_KEYS * chunks_per_row; idx += LT_THREADS) {
+    for (int idx = threadIdx.x; idx < LT_KEYS * chunks_per_row; idx += LT_THREADS * G) {
       const int kk = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
       const bool ok = j0 + kk <= plast;
       cp_async16((uint32_t)__cvta_generic_to_shared(cs + kk * LDC + c), ok ? (const void*)(cbase + (j0 + kk) * R + c) : (const void*)cbase, ok);
@@ -164,7 +169,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    {   // ---- S
+    if (active) {   // ---- S
       float sc[2][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
@@ -187,8 +192,8 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
         }
     }
     __syncthreads();
-    {   // ---- P: thread = (row, eighth of the chunk)
-      const int r = threadIdx.x >> 3, seg = threadIdx.x & 7;
+    if (active) {   // ---- P: thread = (row, eighth of the chunk)
+      const int r = tl >> 3, seg = tl & 7;
       float v[8], mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 8; ++i) { v[i] = ss[r * 68 + seg * 8 + i]; mx = fmaxf(mx, v[i]); }
@@ -215,7 +220,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
       }
     }
     __syncthreads();
-    {   // ---- O
+    if (active) {   // ---- O
       const float c0 = row_c[lane >> 2], c1 = row_c[(lane >> 2) + 8];
 #pragma unroll
       for (int i = 0; i < LT_MAX_NT; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
@@ -299,21 +304,34 @@ extern "C" int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap
   }
 }
 
+static int g_lt_groups = 0;     // 0: chosen per launch; 1..4: forced (b200p_latent_attn_set_groups)
+
 template <typename T>
 static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                    const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                                    cudaStream_t st) {
-  const size_t smem = ((size_t)(LT_KEYS + LT_ROWS) * (R + 8) + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
-  auto kern = latent_attn_tile_kernel<T>;
+  const int by_head = max_n == 1 ? 1 : 0;       // one token per entry: tile over the heads instead of over the tokens
+  const int units = by_head ? (H + LT_ROWS - 1) / LT_ROWS : H;                   // 16-row tiles that share one set of keys
+  // Two tiles per CTA halve the L2 -> shared traffic per head and win on prompts from rank 128 up (1.1x at rank 256, 1.8x at
+  // rank 512); four leave one CTA per SM (registers) and lose the overlap between CTAs again.  Decode steps gain nothing.
+  int G = g_lt_groups > 0 ? g_lt_groups : (by_head || R < 128) ? 1 : 2;
+  if (G > units) G = units;
+  if (G == 3) G = 2;
+  const size_t group_bytes = ((size_t)LT_ROWS * (R + 8) + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
+  const size_t smem = (size_t)LT_KEYS * (R + 8) * sizeof(T) + G * group_bytes;
+  auto kern = G == 1 ? latent_attn_tile_kernel<T, 1> : G == 2 ? latent_attn_tile_kernel<T, 2> : latent_attn_tile_kernel<T, 4>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(latent_attn_tile_kernel)");
   }
-  const int by_head = max_n == 1 ? 1 : 0;       // one token per entry: tile over the heads instead of over the tokens
-  dim3 grid(by_head ? 1u : (unsigned)((max_n + LT_ROWS - 1) / LT_ROWS), by_head ? (unsigned)((H + LT_ROWS - 1) / LT_ROWS) : (unsigned)H,
-            (unsigned)nb);
-  kern<<<grid, LT_THREADS, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head);
+  dim3 grid(by_head ? 1u : (unsigned)((max_n + LT_ROWS - 1) / LT_ROWS), (unsigned)((units + G - 1) / G), (unsigned)nb);
+  kern<<<grid, LT_THREADS * G, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head);
   B200P_LAUNCH_CHECK("latent_attn_tile_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_attn_set_groups(int groups) {
+  g_lt_groups = groups < 0 ? 0 : groups > LT_MAX_GROUPS ? LT_MAX_GROUPS : groups;
   return B200P_OK;
 }
 
