@@ -514,3 +514,91 @@ def test_latent_attention_decode_tiles_over_heads(H, R, window):
         keys = c64[rows[t], lo:pos[t] + 1]
         want = (torch.softmax(q[t].double() @ keys.T * 0.3, -1) @ keys).reshape(-1)
         assert (single[t].double().cpu() - want).abs().max() < 0.02 and (tiles[t].double().cpu() - want).abs().max() < 0.04
+
+
+def test_latent_attention_tiles_sharing_keys_between_heads():
+    """One, two or four 16-row tiles per CTA read the same staged keys: identical numbers, also when the head count leaves
+    groups of the last CTA without a head."""
+    from mlx_parallm_b200 import _lib, ops
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(3)
+    H, R, window, nb, T = 5, 128, 21, 2, 37
+    cache = (torch.randn(nb, 64, R, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    q = (torch.randn(nb * T, H * R, generator=g) * 0.3).cuda()
+    i32 = dict(dtype=torch.int32, device="cuda")
+    t_row = torch.arange(nb, **i32).repeat_interleave(T)
+    t_pos = torch.arange(T, **i32).repeat(nb) + 9
+    outs = []
+    try:
+        for groups in (1, 2, 4, 0):
+            L.b200p_latent_attn_set_groups(groups)
+            out = torch.empty(nb * T, H * R, dtype=torch.bfloat16, device="cuda")
+            ops.latent_attn(q, cache, t_row, t_pos, out, H, R, window, 0.2, cu=torch.tensor([0, T, 2 * T], **i32), rows=torch.arange(nb, **i32),
+                            nb=nb, max_n=T)
+            outs.append(out)
+    finally:
+        L.b200p_latent_attn_set_groups(0)
+    single = torch.empty_like(outs[0])
+    ops.latent_attn(q, cache, t_row, t_pos, single, H, R, window, 0.2)
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+    assert (outs[0].float() - single.float()).abs().max() < 0.03
+
+
+def test_latent_attention_rank_above_the_tile_kernel():
+    """Rank 640 runs on the per-token kernel (the tile kernel stops at 512)."""
+    from mlx_parallm_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    H, R, window, T = 2, 640, 6, 19
+    cache = (torch.randn(1, 32, R, generator=g) * 0.2).to(torch.bfloat16)
+    q = torch.randn(T, H, R, generator=g) * 0.2
+    i32 = dict(dtype=torch.int32, device="cuda")
+    t_row, t_pos = torch.zeros(T, **i32), torch.arange(T, **i32) + 4
+    out = torch.empty(T, H * R, dtype=torch.bfloat16, device="cuda")
+    ops.latent_attn(q.reshape(T, H * R).cuda().contiguous(), cache.cuda(), t_row, t_pos, out, H, R, window, 0.25,
+                    cu=torch.tensor([0, T], **i32), rows=torch.zeros(1, **i32), nb=1, max_n=T)
+    c64 = cache[0].double()
+    for t in range(T):
+        p = t + 4
+        keys = c64[max(0, p - window + 1):p + 1]
+        want = (torch.softmax(q[t].double() @ keys.T * 0.25, -1) @ keys).reshape(-1)
+        assert (out[t].double().cpu() - want).abs().max() < 0.02
+
+
+@pytest.mark.parametrize("dk,dv,H,KH", [(16, 100, 2, 1), (128, 64, 4, 2), (200, 24, 2, 2), (300, 70, 3, 1)])
+def test_delta_scan_key_and_value_sizes(dk, dv, H, KH):
+    """The recurrence kernel alone against a float64 loop: key sizes that put 4, 8 and 16 lanes on a column, value sizes that
+    leave column slots empty or need several thread blocks; one entry continues a stored state, one starts from nothing."""
+    import ctypes as C
+    from mlx_parallm_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(dk + dv)
+    counts, rows, lengths = [11, 3], [2, 0], [5, 0]
+    M = sum(counts)
+    qn = torch.randn(M, KH, dk, generator=g) / dk
+    kn = torch.nn.functional.normalize(torch.randn(M, KH, dk, generator=g), dim=-1)
+    v = torch.randn(M, H, dv, generator=g)
+    beta, decay = torch.rand(M, H, generator=g), 0.5 + 0.5 * torch.rand(M, H, generator=g)
+    state0 = torch.randn(3, H, dk, dv, generator=g) * 0.3
+    want_o, want_s = torch.zeros(M, H, dv, dtype=torch.float64), state0.double().clone()
+    t = 0
+    for n, r, ln in zip(counts, rows, lengths):
+        for h in range(H):
+            S = want_s[r, h].clone() if ln > 0 else torch.zeros(dk, dv, dtype=torch.float64)
+            for i in range(t, t + n):
+                k, q_ = kn[i, h // (H // KH)].double(), qn[i, h // (H // KH)].double()
+                S = S * decay[i, h].double()
+                u = beta[i, h].double() * (v[i, h].double() - S.T @ k)
+                S = S + torch.outer(k, u)
+                want_o[i, h] = S.T @ q_
+            want_s[r, h] = S
+        t += n
+    i32 = dict(dtype=torch.int32, device="cuda")
+    dev = [x.contiguous().cuda() for x in (qn.reshape(M, -1), kn.reshape(M, -1), v.reshape(M, -1), beta, decay, state0)]
+    cu, rw, ln = torch.tensor([0, counts[0], M], **i32), torch.tensor(rows, **i32), torch.tensor([0, 0, 5], **i32)
+    o = torch.empty(M, H * dv, device="cuda")
+    p = lambda x: C.c_void_p(x.data_ptr())
+    assert L.b200p_delta_scan(p(dev[0]), p(dev[1]), p(dev[2]), p(dev[3]), p(dev[4]), p(dev[5]), p(cu), p(rw), p(ln), p(o), 2, H, KH, dk, dv,
+                              None) == 0
+    assert (o.double().cpu().view(M, H, dv) - want_o).abs().max() < 1e-4
+    assert (dev[5].double().cpu()[[0, 2]] - want_s[[0, 2]]).abs().max() < 1e-4
+    assert torch.equal(dev[5].cpu()[1], state0[1])               # a row that no entry names is not touched
