@@ -280,8 +280,9 @@ int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int6
                int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype, int epilogue, float limit,
                void* stream);
 
-/* 0 (default): calls of more than 16 rows run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators) and fall back
- * to the mma.sync kernels for shapes it declines (K < 64); 1: mma.sync kernels only; 2: tcgen05 from 9 rows. */
+/* 0 (default): calls of 9 rows and more run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators; up to 64 rows with the
+ * weights on the MMA's M side and K split where the output is narrow, which adds fp32 partial sums in no fixed order) and fall
+ * back to the mma.sync kernels for shapes it declines (K < 64); 1: mma.sync kernels only; 2: the same as 0. */
 int b200p_gemm_set_path(int path);
 /* 0, or 1 + the role (0 loader, 1 MMA issuer, 2 epilogue) whose bounded barrier wait ran out in a tcgen05 dense GEMM since the
  * last call (which clears it).  Synchronises the device. */

@@ -1,8 +1,8 @@
 // Dense (unquantised) linear layers: y[M,N] = x[M,K] . w[N,K]^T with fp32 accumulation, optionally batched over a leading
 // index (one weight block per attention head).  Five kernels behind b200p_gemm:
-//   gemm_tc_kernel     16-bit operands, tcgen05 / TMA / TMEM (dense_gemm_tc.cu)                             (more than 16 rows)
+//   gemm_tc_kernel     16-bit operands, tcgen05 / TMA / TMEM (dense_gemm_tc.cu)                             (9 rows and more)   
 //   gemm_mma_kernel    16-bit operands, mma.sync m16n8k16 over cp.async-staged tiles, two tile shapes      (K < 64, or on request)
-//   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..16 rows: decode)
+//   gemm_stream_kernel 16-bit operands, weights streamed from global memory straight into MMA fragments    (9..64 rows where tcgen05 declines)
 //   gemv_rows_kernel   16-bit operands, a warp per pair of weight rows, 128-bit streaming                  (up to 8 rows)
 //   gemm_simt_kernel   any operand type and any shape or alignment; true fp32 FMA in ascending k for float32 models
 // Epilogues: store in the storage type, store fp32, and the clamped gated unit of b200p.h (gate / up rows interleaved).
@@ -17,8 +17,8 @@ namespace b200p {
 template <typename T>
 int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
                    int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st);
-// 0: tcgen05 above 16 rows (at 32 rows it already streams the weights 1.2-1.5x faster than gemm_stream_kernel, at 64 rows 2-3x),
-//    the mma.sync kernels where it declines; 1: mma.sync kernels only; 2: tcgen05 from 9 rows
+// 0: tcgen05 from 9 rows up (its decode variant streams the weights 1.0-2.3x faster than gemm_stream_kernel at 16 rows, 1.1-2.6x at
+//    32, 1.6-4.4x at 64), the mma.sync kernels where it declines; 1: mma.sync kernels only; 2: the same as 0
 static int g_gemm_path = 0;
 
 // ---- epilogue -------------------------------------------------------------------------------------------------------
@@ -345,7 +345,7 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
   }
   if (fast_ok) {
     if constexpr (!std::is_same<T, float>::value) {
-      if (M <= 64 && g_gemm_path != 1 && (M > 16 || g_gemm_path == 2)) {
+      if (M <= 64 && g_gemm_path != 1) {
         const int rc = gemm_tc_launch<T>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
         if (rc != 1) return rc;
       }

@@ -13,6 +13,13 @@
 //               stage; owns the TMEM allocation
 //   warps 2..5  epilogue: tcgen05.ld (thread = token row, 32 columns at a time) -> store / store fp32 / clamped gated unit
 //
+// Decode batches (17..64 tokens) swap the operands: the weight tile is the 128-row M side, the tokens are the narrow N side
+// (BN = 32 or 64), because the MMA reads all 128 rows of its A operand from shared memory whatever they hold, and with the
+// tokens there that read (not HBM) bounded the weight stream.  The accumulator then holds y transposed (lane = output column,
+// TMEM column = token) and the epilogue stores it back transposed, a warp writing 32 consecutive outputs of one token.  Where
+// the weight matrix has too few 128-row tiles to fill the GPU (narrow outputs with long K), K is split over several CTAs that
+// add their partial sums into the zeroed fp32 output with red.global.add.
+//
 // Rows, columns and k outside the tensors are zero-filled by the TMA unit and masked in the epilogue.  Every mbarrier wait is
 // bounded: a wait that runs out raises a device flag (reported by the next launch) and the CTA leaves through the common exit,
 // which frees its TMEM.
@@ -36,6 +43,8 @@ struct GemmTcParams {
   void* y;
   int64_t M, N, K, ldy, sy;
   int tiles_m, tiles_n, num_tiles, num_kb;
+  int splits, kb_per_split;      // K split over `splits` CTAs per output tile (transposed fp32 store only)
+  int trans;                     // operands swapped: accumulator row = output column, accumulator column = token
   int epi, vec_ok;
   float limit;
 };
@@ -126,8 +135,44 @@ __device__ __forceinline__ void gemm_tc_store32(const GemmTcParams& p, int64_t r
   }
 }
 
+// Swapped operands: this thread owns output column `n` (a weight row) and holds it for 32 consecutive tokens from `tok0`.
+// p.M counts output columns and p.N tokens here.  Gate / up pairs sit in neighbouring lanes.
+template <typename T>
+__device__ __forceinline__ void gemm_tc_store32_trans(const GemmTcParams& p, int64_t z_off, int64_t n, int64_t tok0, const float (&v)[32]) {
+  if (p.epi == B200P_GEMM_GLU_CLAMP) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+      if (!(threadIdx.x & 1) && n + 1 < p.M && tok0 + i < p.N) {
+        const float g = fminf(v[i], p.limit);
+        const float u = fminf(fmaxf(other, -p.limit), p.limit);
+        reinterpret_cast<T*>(p.y)[z_off + (tok0 + i) * p.ldy + (n >> 1)] = Tr<T>::from_f(g / (1.f + __expf(-1.702f * g)) * (u + 1.f));
+      }
+    }
+    return;
+  }
+  if (n >= p.M) return;
+  if (p.epi == B200P_GEMM_STORE_F32) {
+    float* dst = reinterpret_cast<float*>(p.y) + z_off + n;
+    if (p.splits > 1) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (tok0 + i < p.N) atomicAdd(dst + (tok0 + i) * p.ldy, v[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (tok0 + i < p.N) dst[(tok0 + i) * p.ldy] = v[i];
+    }
+  } else {
+    T* dst = reinterpret_cast<T*>(p.y) + z_off + n;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (tok0 + i < p.N) dst[(tok0 + i) * p.ldy] = Tr<T>::from_f(v[i]);
+  }
+}
+
 struct GemmTcShared {            // lives behind the ring stages (8-byte aligned)
-  uint64_t full[8], empty[8], acc_full[2], acc_empty[2];
+  uint64_t full[10], empty[10], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   volatile int abort;
 };
@@ -160,8 +205,8 @@ template <typename T, int BN, int STAGES>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw, const GemmTcParams p) {
   constexpr int B_BYTES = BN * GT_BK * 2, STAGE_BYTES = GT_A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = 2 * BN;           // 128, 256 or 512: a power of two >= 32
-  static_assert(STAGES <= 8 && (BN == 64 || BN == 128 || BN == 256), "ring / tile shape");
+  constexpr uint32_t TMEM_COLS = 2 * BN;           // 64 .. 512: a power of two >= 32
+  static_assert(STAGES <= 10 && (BN == 32 || BN == 64 || BN == 128 || BN == 256), "ring / tile shape");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;    // SWIZZLE_128B tiles start on 1024-byte boundaries
@@ -197,9 +242,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const int z = t / per_batch, r = t - z * per_batch;
+        const int ts = t / p.splits, kb0 = (t - ts * p.splits) * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        const int z = ts / per_batch, r = ts - z * per_batch;
         const int nt = r / p.tiles_m, mt = r - nt * p.tiles_m;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = gemm_tc_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, sh, 0))) break;
           const uint32_t bar = smem_u32(&sh->full[stage]);
           const uint32_t dst = base + stage * STAGE_BYTES;
@@ -221,14 +268,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         if (!(ok = gemm_tc_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, sh, 1))) break;
         tc_fence_after();
         const uint32_t d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int kb0 = (t % p.splits) * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = gemm_tc_wait(smem_u32(&sh->full[stage]), phase, sh, 1))) break;
           tc_fence_after();
           const uint64_t ad = make_desc_sw128(base + stage * STAGE_BYTES);
           const uint64_t bd = make_desc_sw128(base + stage * STAGE_BYTES + GT_A_BYTES);
 #pragma unroll
           for (int k = 0; k < GT_BK / 16; ++k)     // 16 k = 32 bytes = 2 descriptor units inside the swizzle atom
-            umma_f16_ss(d, ad + 2u * k, bd + 2u * k, idesc, (kb | k) ? 1u : 0u);
+            umma_f16_ss(d, ad + 2u * k, bd + 2u * k, idesc, ((kb - kb0) | k) ? 1u : 0u);
           umma_commit(smem_u32(&sh->empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -242,7 +290,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
-      const int z = t / per_batch, r = t - z * per_batch;
+      const int ts = t / p.splits;
+      const int z = ts / per_batch, r = ts - z * per_batch;
       const int nt = r / p.tiles_m, mt = r - nt * p.tiles_m;
       if (!gemm_tc_wait(smem_u32(&sh->acc_full[acc]), acc_phase, sh, 2)) break;
       tc_fence_after();
@@ -257,7 +306,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         tmem_ld16(tsrc + c, *reinterpret_cast<float(*)[16]>(&v[0]));
         tmem_ld16(tsrc + c + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
         tmem_ld_wait();
-        if (row < p.M) gemm_tc_store32<T>(p, row_off, n0, v);
+        if (p.trans) gemm_tc_store32_trans<T>(p, (int64_t)z * p.sy, row, n0, v);
+        else if (row < p.M) gemm_tc_store32<T>(p, row_off, n0, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -312,6 +362,44 @@ static int gemm_tc_run(const CUtensorMap& tmx, const CUtensorMap& tmw, GemmTcPar
   return B200P_OK;
 }
 
+// Up to 64 tokens: weights on the M side, tokens on the N side, transposed store, K split where the output is narrow.
+template <typename T>
+static int gemm_tc_launch_decode(TcEncodeFn enc, const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                                 int64_t ldy, int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st) {
+  const CUtensorMapDataType dt = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int bn = M <= 32 ? 32 : 64;
+  CUtensorMap tma, tmb;                            // A = weights (128-row boxes), B = tokens (bn-row boxes)
+  if (!gemm_tc_map(enc, &tma, dt, w, K, N, batch, ldw, sw, GT_BM)) return 1;
+  if (!gemm_tc_map(enc, &tmb, dt, x, K, M, batch, ldx, sx, bn)) return 1;
+  GemmTcParams p;
+  p.y = y;
+  p.M = N; p.N = M; p.K = K; p.ldy = ldy; p.sy = sy;
+  p.tiles_m = (int)((N + GT_BM - 1) / GT_BM);
+  p.tiles_n = 1;
+  p.num_kb = (int)((K + GT_BK - 1) / GT_BK);
+  const int64_t tiles = (int64_t)p.tiles_m * batch;
+  if (tiles >= (1ll << 24)) return 1;
+  // few weight tiles and a long K: split K so that about one CTA per SM streams weights, at least 4 k-blocks each
+  int splits = 1;
+  if (epi == B200P_GEMM_STORE_F32 && batch == 1 && ldy == N && tiles * 2 <= sm_count()) {
+    splits = (int)min((int64_t)(sm_count() / tiles), (int64_t)(p.num_kb / 4));
+    if (splits < 1) splits = 1;
+  }
+  p.kb_per_split = (p.num_kb + splits - 1) / splits;
+  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;          // no empty split
+  p.num_tiles = (int)(tiles * p.splits);
+  p.trans = 1;
+  p.epi = epi;
+  p.limit = limit;
+  p.vec_ok = 0;
+  if (p.splits > 1) {
+    cudaError_t e = cudaMemsetAsync(y, 0, (size_t)M * N * sizeof(float), st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(split-K output)");
+  }
+  if (bn == 32) return gemm_tc_run<T, 32, 10>(tma, tmb, p, st);
+  return gemm_tc_run<T, 64, 8>(tma, tmb, p, st);
+}
+
 // Returns B200P_OK, an error, or 1 when the shape is not one this kernel takes (the caller then runs the mma.sync kernel).
 template <typename T>
 int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
@@ -319,6 +407,7 @@ int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_
   if (K < GT_BK || M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return 1;
   TcEncodeFn enc = gemm_tc_encode_fn();
   if (!enc) return 1;
+  if (M <= 64) return gemm_tc_launch_decode<T>(enc, x, w, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
   const int tiles_m = (int)((M + GT_BM - 1) / GT_BM);
   // widest weight tile that still gives every SM about two tiles
   const int64_t want = 2ll * sm_count();
@@ -338,6 +427,9 @@ int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_
   if (nt >= (1ll << 31)) return 1;
   p.num_tiles = (int)nt;
   p.num_kb = (int)((K + GT_BK - 1) / GT_BK);
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.trans = 0;
   p.epi = epi;
   p.limit = limit;
   const int64_t eb = epi == B200P_GEMM_STORE_F32 ? 4 : 2;

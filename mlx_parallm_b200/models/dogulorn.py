@@ -32,9 +32,10 @@ class ModelArgs(BaseModelArgs):
     def __post_init__(self):
         if not self.layers:
             raise ValueError("config 'layers' is empty")
-        extra = set(self.norm) - {"eps"}
-        if extra:
-            raise NotImplementedError(f"norm options {sorted(extra)} are not part of this design (an rms norm with a weight)")
+        kind = str(self.norm.get("kind", self.norm.get("type", "rms"))).lower().replace("_", "").replace("norm", "")
+        extra = set(self.norm) - {"eps", "kind", "type"}
+        if extra or kind != "rms":
+            raise NotImplementedError(f"norm options {sorted(extra) or kind!r} are not part of this design (an rms norm with a weight)")
         for i, L in enumerate(self.layers):
             if L.get("type") not in ("delta", "latent_attention"):
                 raise NotImplementedError(f"layer {i}: mixer type {L.get('type')!r} is not part of this design")

@@ -102,10 +102,12 @@ def test_gemm_gated_epilogue_and_heads(dtype, M):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,N,K", [(17, 72, 64), (40, 264, 200), (64, 520, 128), (65, 8, 64), (128, 72, 72), (300, 264, 200), (1000, 520, 512), (129, 1100, 64), (4100, 640, 136)])
+@pytest.mark.parametrize("M,N,K", [(9, 130, 72), (17, 72, 64), (40, 264, 200), (64, 520, 128), (65, 8, 64), (128, 72, 72), (300, 264, 200), (1000, 520, 512), (129, 1100, 64), (4100, 640, 136),
+                                   (33, 9700, 64), (20, 9500, 200), (32, 2048, 2080), (50, 1000, 1700)])
 def test_gemm_tcgen05_tiles(dtype, M, N, K):
-    """More than 64 rows with K >= 64 run on tcgen05: ragged tile edges in all three dimensions, every tile width, all epilogues,
-    against float64 and against the mma.sync kernel."""
+    """Nine rows and more with K >= 64 run on tcgen05: ragged tile edges in all three dimensions, every tile width, all epilogues,
+    against float64 and against the mma.sync kernel.  Up to 64 rows take the decode variant (weights on the M side, a 32- or
+    64-token N side, transposed store, K split over several CTAs where the output is narrow and K long)."""
     from mlx_parallm_b200 import _lib, ops
     L = _lib.lib()
     g = torch.Generator().manual_seed(M + N + K)
@@ -131,11 +133,12 @@ def test_gemm_tcgen05_tiles(dtype, M, N, K):
         assert glu.shape == (M, N // 2) and (glu.double() - a * torch.sigmoid(1.702 * a) * (u + 1)).abs().max() < 0.02
 
 
-def test_gemm_tcgen05_heads_and_strides():
+@pytest.mark.parametrize("M", [330, 24, 57])
+def test_gemm_tcgen05_heads_and_strides(M):
     """One weight block per head, operands and outputs strided inside wider rows (3-d tensor maps)."""
     from mlx_parallm_b200 import _lib, ops
     g = torch.Generator().manual_seed(11)
-    M, H, dk, R = 330, 3, 64, 40
+    H, dk, R = 3, 64, 40
     q = (torch.randn(M, H * dk, generator=g) / 4).to(torch.bfloat16).cuda()
     wk = (torch.randn(H, R, dk, generator=g) / 4).to(torch.bfloat16).cuda()
     want = torch.einsum("mhd,hrd->mhr", q.double().view(M, H, dk), wk.double()).reshape(M, H * R)
