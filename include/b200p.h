@@ -353,6 +353,9 @@ int b200p_latent_attn_tiles_supported(int R, int dtype);
 /* 16-row tiles (heads of a prompt tile, or blocks of 16 heads of a decode step) that one CTA of the tile kernel serves from one
  * staged copy of the keys: 1..4, or 0 for the built-in choice. */
 int b200p_latent_attn_set_groups(int groups);
+/* CTAs of a thread-block cluster that share the keys of one decode tile (each a run of 64-key chunks, merged through distributed
+ * shared memory): 2, 4 or 8, 1 for one CTA per tile, 0 for the built-in choice (about two CTAs per SM). */
+int b200p_latent_attn_set_splits(int splits);
 int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                             const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                             int dtype, void* stream);

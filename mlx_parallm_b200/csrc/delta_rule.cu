@@ -15,7 +15,8 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 
 constexpr int DELTA_MAX_TAPS = 16;
 
-__global__ void __launch_bounds__(1024)
+template <int NT>
+__global__ void __launch_bounds__(NT)
 delta_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* __restrict__ conv_w,
                   const float* __restrict__ conv_state, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                   const int32_t* __restrict__ t_row, const int32_t* __restrict__ t_pos, const int32_t* __restrict__ t_off,
@@ -266,10 +267,12 @@ extern "C" int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, i
   const size_t smem = (size_t)2 * KH * dk * sizeof(float);
   B200P_REQUIRE(smem <= 48 * 1024, B200P_ERR_ARG, "q and k of one token must fit 48 KB of shared memory");
   // a decode batch has few tokens and thousands of channels each: wider blocks shorten the per-thread channel loop
-  const unsigned threads = M <= 256 ? 1024u : 256u;
-  delta_prep_kernel<<<(unsigned)M, threads, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias,
-                                                                      t_row, t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv,
-                                                                      taps);
+  if (M <= 256)
+    delta_prep_kernel<1024><<<(unsigned)M, 1024, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row,
+                                                                               t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps);
+  else
+    delta_prep_kernel<256><<<(unsigned)M, 256, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row,
+                                                                             t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps);
   B200P_LAUNCH_CHECK("delta_prep_kernel");
   return B200P_OK;
 }

@@ -7,6 +7,8 @@
 //   latent_attn_tile_kernel  16-bit models: up to four tiles of 16 query rows per CTA (prompts: 16 consecutive tokens of one
 //                        sequence for one head each; decode steps: 16 heads each of the one new token), mma.sync m16n8k16 for
 //                        q.c and p.c over 64-key chunks staged once for both products and for all the CTA's tiles
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -119,12 +121,16 @@ latent_attn_kernel(const float* __restrict__ q, const T* __restrict__ cache, int
 constexpr int LT_ROWS = 16, LT_KEYS = 64, LT_THREADS = 128, LT_MAX_NT = 16;      // R <= 512, R % 32 == 0
 constexpr int LT_MAX_GROUPS = 4;
 
+int sm_count();
+
 template <typename T, int G>
 __global__ void __launch_bounds__(LT_THREADS * G)
 latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache, int64_t Tcap, const int32_t* __restrict__ cu,
                         const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos, T* __restrict__ out, int H, int R,
-                        int64_t window, float scale, int by_head) {
+                        int64_t window, float scale, int by_head, int splits) {
   extern __shared__ __align__(128) uint8_t lt_smem[];
+  // splits > 1 (decode only): the CTAs of a thread-block cluster (gridDim.x = cluster size = splits) share the keys of one tile
+  // between them, a run of 64-key chunks each, and CTA 0 merges their partial sums through distributed shared memory
   // by_head == 0: rows of a group's tile are 16 consecutive tokens of entry e = blockIdx.z, for ONE head (prompts)
   // by_head == 1: rows are 16 consecutive heads of the ONE token of entry e (decode: every head reads the same keys)
   const int e = blockIdx.z;
@@ -159,7 +165,13 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
 #pragma unroll
   for (int i = 0; i < LT_MAX_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const int chunks_per_row = R / 8;
-  for (int64_t j0 = kmin; j0 <= plast; j0 += LT_KEYS) {
+  int64_t jbeg = kmin, jend = plast;                             // this CTA's keys, inclusive
+  if (splits > 1) {
+    const int64_t nchunks = (plast - kmin) / LT_KEYS + 1, per = (nchunks + splits - 1) / splits;
+    jbeg = kmin + (int64_t)blockIdx.x * per * LT_KEYS;
+    jend = min(plast, jbeg + per * LT_KEYS - 1);
+  }
+  for (int64_t j0 = jbeg; j0 <= jend; j0 += LT_KEYS) {
     __syncthreads();                                             // the previous chunk's products are done with cs / ss / ps
     for (int idx = threadIdx.x; idx < LT_KEYS * chunks_per_row; idx += LT_THREADS * G) {
       const int kk = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
@@ -241,6 +253,44 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     }
   }
   __syncthreads();
+  if (splits > 1) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    float* po = reinterpret_cast<float*>(cs);                    // [16][R] unnormalised partial sums (the chunk buffer is free now)
+#pragma unroll
+    for (int i = 0; i < LT_MAX_NT; ++i) {
+      if (i < ntw) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = (lane >> 2) + hf * 8, c = warp * (R / 4) + i * 8 + (lane & 3) * 2;
+          po[r * R + c] = o[i][hf * 2];
+          po[r * R + c + 1] = o[i][hf * 2 + 1];
+        }
+      }
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0) {
+      const int r = tl >> 3, seg = tl & 7;                       // eight threads per row
+      if (r < nrow) {
+        float m = -INFINITY, l = 0.f, w[8];
+        for (int s_ = 0; s_ < splits; ++s_) m = fmaxf(m, cluster.map_shared_rank(row_m, s_)[r]);
+        for (int s_ = 0; s_ < splits; ++s_) {
+          const float ms = cluster.map_shared_rank(row_m, s_)[r];
+          w[s_] = ms == -INFINITY ? 0.f : __expf(ms - m);       // a CTA whose run of keys was empty or all masked
+          l += cluster.map_shared_rank(row_l, s_)[r] * w[s_];
+        }
+        const float inv = 1.f / l;
+        T* dst = out + ((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R;
+        for (int c = seg; c < R; c += 8) {
+          float acc = 0.f;
+          for (int s_ = 0; s_ < splits; ++s_) acc += cluster.map_shared_rank(po, s_)[r * R + c] * w[s_];
+          dst[c] = Tr<T>::from_f(acc * inv);
+        }
+      }
+    }
+    cluster.sync();                                              // the other CTAs' shared memory lives until CTA 0 has read it
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < LT_MAX_NT; ++i) {
     if (i < ntw) {
@@ -305,6 +355,7 @@ extern "C" int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap
 }
 
 static int g_lt_groups = 0;     // 0: chosen per launch; 1..4: forced (b200p_latent_attn_set_groups)
+static int g_lt_splits = 0;     // decode: 0 = chosen per launch; 1 = one CTA per tile; 2, 4, 8 = forced (b200p_latent_attn_set_splits)
 
 template <typename T>
 static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
@@ -324,14 +375,46 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(latent_attn_tile_kernel)");
   }
-  dim3 grid(by_head ? 1u : (unsigned)((max_n + LT_ROWS - 1) / LT_ROWS), (unsigned)((units + G - 1) / G), (unsigned)nb);
-  kern<<<grid, LT_THREADS * G, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head);
+  // Decode steps have few tiles (entries x heads / 16), each a serial walk over the window: a cluster of up to 8 CTAs shares the
+  // chunks of one tile so that about two CTAs per SM stream the cache
+  int splits = 1;
+  if (by_head && G == 1 && g_lt_splits != 1) {
+    const int64_t tiles = (int64_t)nb * units, span = window > 0 ? window : Tcap;
+    const int64_t chunks = (span + LT_KEYS - 1) / LT_KEYS + 1;
+    int64_t want = g_lt_splits > 1 ? g_lt_splits : (2ll * sm_count() + tiles - 1) / tiles;
+    want = want < chunks ? want : chunks;
+    splits = want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
+  }
+  dim3 grid(by_head ? (unsigned)splits : (unsigned)((max_n + LT_ROWS - 1) / LT_ROWS), (unsigned)((units + G - 1) / G), (unsigned)nb);
+  if (splits > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(LT_THREADS * G);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)splits;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, splits);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(latent_attn_tile_kernel)");
+  } else {
+    kern<<<grid, LT_THREADS * G, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, 1);
+  }
   B200P_LAUNCH_CHECK("latent_attn_tile_kernel");
   return B200P_OK;
 }
 
 extern "C" int b200p_latent_attn_set_groups(int groups) {
   g_lt_groups = groups < 0 ? 0 : groups > LT_MAX_GROUPS ? LT_MAX_GROUPS : groups;
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_attn_set_splits(int splits) {
+  g_lt_splits = splits < 0 ? 0 : splits > 8 ? 8 : splits;
   return B200P_OK;
 }
 

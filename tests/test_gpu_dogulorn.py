@@ -496,11 +496,15 @@ def test_latent_attention_tile_kernel(R, window):
         assert (seen - hot).norm() < 0.2 * hot.norm() and (unseen - hot).norm() > 0.6 * hot.norm()
 
 
-@pytest.mark.parametrize("H,R,window", [(20, 64, 33), (8, 128, 0), (16, 32, 64)])
-def test_latent_attention_decode_tiles_over_heads(H, R, window):
+@pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("H,R,window", [(20, 64, 33), (8, 128, 0), (16, 32, 64), (3, 512, 130)])
+def test_latent_attention_decode_tiles_over_heads(H, R, window, splits):
     """A decode step (one token per entry) tiles over the heads of each token: against float64 and against the per-token
-    kernel, entries at different positions (also position 0), a head count that leaves the last tile partial."""
-    from mlx_parallm_b200 import ops
+    kernel, entries at different positions (also position 0), a head count that leaves the last tile partial.  With the keys
+    of a tile shared between the CTAs of a cluster (2, 4, 8; 0 = the launch's own choice), some of which get no key at all
+    at the early positions."""
+    from mlx_parallm_b200 import _lib, ops
+    L = _lib.lib()
     g = torch.Generator().manual_seed(H + R)
     pos, rows = [0, 1, 63, 64, 150], [1, 4, 0, 3, 2]
     cache = (torch.randn(5, 160, R, generator=g) * 0.3).to(torch.bfloat16)
@@ -509,7 +513,11 @@ def test_latent_attention_decode_tiles_over_heads(H, R, window):
     t_row, t_pos = torch.tensor(rows, **i32), torch.tensor(pos, **i32)
     cd, qd = cache.cuda(), q.reshape(5, H * R).cuda().contiguous()
     tiles, single = torch.empty(5, H * R, dtype=torch.bfloat16, device="cuda"), torch.empty(5, H * R, dtype=torch.bfloat16, device="cuda")
-    ops.latent_attn(qd, cd, t_row, t_pos, tiles, H, R, window, 0.3, cu=torch.arange(6, **i32), rows=t_row, nb=5, max_n=1)
+    L.b200p_latent_attn_set_splits(splits)
+    try:
+        ops.latent_attn(qd, cd, t_row, t_pos, tiles, H, R, window, 0.3, cu=torch.arange(6, **i32), rows=t_row, nb=5, max_n=1)
+    finally:
+        L.b200p_latent_attn_set_splits(0)
     ops.latent_attn(qd, cd, t_row, t_pos, single, H, R, window, 0.3)
     c64 = cache.double()
     for t in range(5):
