@@ -465,12 +465,12 @@ def _gemm_rooflines(prof, rows, w_bytes_per_el, tflops, hbm_gbs):
     import re
     out = {}
     for k, v in prof.items():
-        m = re.match(r"(b200p_gemm|b200p_qmm)\[N=(\d+),K=(\d+)\]", k)
+        m = re.match(r"(b200p_gemm|b200p_qmm)\[N=(\d+),K=(\d+)(?:,heads=(\d+))?\]", k)
         if not m:
             continue
-        N, K = int(m.group(2)), int(m.group(3))
-        flop_us = 2.0 * rows * N * K / (tflops * 1e12) * 1e6
-        byte_us = (N * K * w_bytes_per_el + rows * (K + N) * 2) / (hbm_gbs * 1e9) * 1e6
+        N, K, heads = int(m.group(2)), int(m.group(3)), int(m.group(4) or 1)      # one weight block per head
+        flop_us = 2.0 * rows * N * K * heads / (tflops * 1e12) * 1e6
+        byte_us = heads * (N * K * w_bytes_per_el + rows * (K + N) * 2) / (hbm_gbs * 1e9) * 1e6
         out[k] = {"mean_us": round(v["mean_us"], 2), "calls": v["calls"], "roofline_us": round(max(flop_us, byte_us), 2),
                   "frac": round(max(flop_us, byte_us) / v["mean_us"], 3), "bound": "tensor" if flop_us > byte_us else "hbm"}
     return out

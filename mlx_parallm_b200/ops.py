@@ -51,7 +51,7 @@ def _call(name: str, rc_fn):
     if PROFILER is None:
         check(rc_fn(), name if isinstance(name, str) else name[0])
         return
-    key = name if isinstance(name, str) else f"{name[0]}[N={name[1]},K={name[2]}]"
+    key = name if isinstance(name, str) else f"{name[0]}[N={name[1]},K={name[2]}" + (f",heads={name[3]}]" if len(name) > 3 and name[3] > 1 else "]")
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     check(rc_fn(), key)
@@ -269,7 +269,7 @@ def gemm(x, w, epilogue=_lib.GEMM_STORE, out=None, limit=0.0, batch=1, strides=(
         ldy = out.stride(0)
     want = torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype
     assert out.dtype == want and out.stride(-1) == 1, (out.dtype, want)
-    _call(("b200p_gemm", N, K), lambda: lib().b200p_gemm(_p(x), _p(w), _p(out), M, N, K, ldx, ldw, ldy, batch, strides[0], strides[1],
+    _call(("b200p_gemm", N, K, batch), lambda: lib().b200p_gemm(_p(x), _p(w), _p(out), M, N, K, ldx, ldw, ldy, batch, strides[0], strides[1],
                                                         strides[2], dtype_code(x.dtype), epilogue, float(limit), _stream()))
     return out
 
