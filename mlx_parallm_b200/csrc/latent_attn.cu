@@ -155,9 +155,12 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
   const int64_t plast = by_head ? p0 : p0 + min(LT_ROWS, cu[e + 1] - t0) - 1;
   const int64_t kmin = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const T* cbase = cache + (int64_t)rows[e] * Tcap * R;
-  for (int idx = tl; idx < LT_ROWS * R; idx += LT_THREADS) {
-    const int r = idx / R, c = idx % R;
-    qs[r * LDC + c] = Tr<T>::from_f(r < nrow ? q[((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R + c] : 0.f);
+#pragma unroll 4
+  for (int idx = tl; idx < LT_ROWS * (R / 4); idx += LT_THREADS) {       // R is a multiple of 32: rows of q are 16-byte aligned
+    const int r = idx / (R / 4), c = (idx % (R / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nrow) v = *reinterpret_cast<const float4*>(q + ((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R + c);
+    *reinterpret_cast<uint2*>(qs + r * LDC + c) = make_uint2(pack2<T>(v.x, v.y), pack2<T>(v.z, v.w));
   }
   if (tl < LT_ROWS) { row_m[tl] = -INFINITY; row_l[tl] = 0.f; }
   const int ntw = R / 32;                                        // 8-column tiles of o per warp
@@ -269,26 +272,41 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
       }
     }
     cluster.sync();
-    if (cluster.block_rank() == 0) {
+    {   // every CTA of the cluster merges its own slice of the columns, R / splits wide, for all rows
       const int r = tl >> 3, seg = tl & 7;                       // eight threads per row
+      const int cw = R / splits, c0 = (int)cluster.block_rank() * cw;
       if (r < nrow) {
-        float m = -INFINITY, l = 0.f, w[8];
-        for (int s_ = 0; s_ < splits; ++s_) m = fmaxf(m, cluster.map_shared_rank(row_m, s_)[r]);
-        for (int s_ = 0; s_ < splits; ++s_) {
-          const float ms = cluster.map_shared_rank(row_m, s_)[r];
-          w[s_] = ms == -INFINITY ? 0.f : __expf(ms - m);       // a CTA whose run of keys was empty or all masked
-          l += cluster.map_shared_rank(row_l, s_)[r] * w[s_];
+        float ms[8], ls[8], m = -INFINITY, l = 0.f;
+#pragma unroll
+        for (int s_ = 0; s_ < 8; ++s_) {
+          if (s_ < splits) {
+            ms[s_] = cluster.map_shared_rank(row_m, s_)[r];
+            ls[s_] = cluster.map_shared_rank(row_l, s_)[r];
+            m = fmaxf(m, ms[s_]);
+          }
+        }
+#pragma unroll
+        for (int s_ = 0; s_ < 8; ++s_) {
+          if (s_ < splits) {
+            ms[s_] = ms[s_] == -INFINITY ? 0.f : __expf(ms[s_] - m);     // a CTA whose run of keys was empty or all masked: 0
+            l += ls[s_] * ms[s_];
+          }
         }
         const float inv = 1.f / l;
         T* dst = out + ((int64_t)(t0 + r * tstep) * H + h + r * hstep) * R;
-        for (int c = seg; c < R; c += 8) {
+#pragma unroll 2
+        for (int c = c0 + seg; c < c0 + cw; c += 8) {
+          float part[8];
+#pragma unroll
+          for (int s_ = 0; s_ < 8; ++s_) part[s_] = s_ < splits ? cluster.map_shared_rank(po, s_)[r * R + c] : 0.f;
           float acc = 0.f;
-          for (int s_ = 0; s_ < splits; ++s_) acc += cluster.map_shared_rank(po, s_)[r * R + c] * w[s_];
+#pragma unroll
+          for (int s_ = 0; s_ < 8; ++s_) acc = fmaf(part[s_], s_ < splits ? ms[s_] : 0.f, acc);
           dst[c] = Tr<T>::from_f(acc * inv);
         }
       }
     }
-    cluster.sync();                                              // the other CTAs' shared memory lives until CTA 0 has read it
+    cluster.sync();                                              // a CTA's shared memory lives until the others have read it
     return;
   }
 #pragma unroll
@@ -428,7 +446,7 @@ extern "C" int b200p_latent_attn_tiles(const float* q, const void* cache, int64_
   B200P_REQUIRE(q && cache && cu && rows && t_pos && out, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(b200p_latent_attn_tiles_supported(R, dtype), B200P_ERR_ARG, "the tile kernel needs a 16-bit type and a rank that is a multiple of 32, at most %d", 32 * LT_MAX_NT);
   B200P_REQUIRE(nb > 0 && nb < 65536 && H > 0 && H < 65536 && max_n > 0, B200P_ERR_ARG, "bad batch geometry");
-  B200P_REQUIRE(aligned(cache, 16) && aligned(out, 4), B200P_ERR_ALIGN, "cache must be 16-byte aligned");
+  B200P_REQUIRE(aligned(cache, 16) && aligned(q, 16) && aligned(out, 4), B200P_ERR_ALIGN, "cache and q must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == B200P_F16) return latent_attn_tile_launch<__half>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
   return latent_attn_tile_launch<__nv_bfloat16>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
