@@ -225,8 +225,8 @@ def dogulorn_config(width: int, ff: int, n_layers: int, heads: int, head_dim: in
         else:
             last_own = i
         layers.append({"type": "latent_attention", "mlp": dict(mlp), "mixer": m})
-    return {"architecture": "Dogulorn", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-5},
-            "embedding": {"scale": 1.0, "bigram": {"buckets": buckets, "mul_prev": 31, "mul_cur": 7}},
+    return {"architecture": "Dogulorn", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": buckets, "mul_prev": 1009, "mul_cur": 13}},
             "token_side": {"dim": side_dim}}
 
 
