@@ -356,6 +356,9 @@ int b200p_latent_attn_set_groups(int groups);
 /* CTAs of a thread-block cluster that share the keys of one decode tile (each a run of 64-key chunks, merged through distributed
  * shared memory): 2, 4 or 8, 1 for one CTA per tile, 0 for the built-in choice (about two CTAs per SM). */
 int b200p_latent_attn_set_splits(int splits);
+/* Chunk buffers of the tile kernel: 2 = the next 64 latents are in flight while the current ones are multiplied, 1 = one buffer,
+ * 0 = the built-in choice (2 where two CTAs per SM still fit beside the buffers). */
+int b200p_latent_attn_set_buffers(int buffers);
 int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                             const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                             int dtype, void* stream);

@@ -81,6 +81,7 @@ SIGNATURES = {
     "b200p_latent_attn": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _f32, _i32, _vp]),
     "b200p_latent_attn_set_groups": (_i32, [_i32]),
     "b200p_latent_attn_set_splits": (_i32, [_i32]),
+    "b200p_latent_attn_set_buffers": (_i32, [_i32]),
     "b200p_latent_attn_tiles_supported": (_i32, [_i32, _i32]),
     "b200p_latent_attn_tiles": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _f32, _i32, _vp]),
 }

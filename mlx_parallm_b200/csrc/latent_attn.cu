@@ -127,7 +127,7 @@ template <typename T, int G>
 __global__ void __launch_bounds__(LT_THREADS * G)
 latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache, int64_t Tcap, const int32_t* __restrict__ cu,
                         const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos, T* __restrict__ out, int H, int R,
-                        int64_t window, float scale, int by_head, int splits) {
+                        int64_t window, float scale, int by_head, int splits, int nbuf) {
   extern __shared__ __align__(128) uint8_t lt_smem[];
   // splits > 1 (decode only): the CTAs of a thread-block cluster (gridDim.x = cluster size = splits) share the keys of one tile
   // between them, a run of 64-key chunks each, and CTA 0 merges their partial sums through distributed shared memory
@@ -142,9 +142,10 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
   const int nrow = !active ? 0 : by_head ? min(LT_ROWS, H - h) : min(LT_ROWS, cu[e + 1] - t0);               // live rows
   const int tstep = by_head ? 0 : 1, hstep = by_head ? 1 : 0;   // row r is token t0 + r * tstep, head h + r * hstep
   const int LDC = R + 8;                                         // padded rows: ldmatrix reads 8 rows without bank conflicts
-  T* cs = reinterpret_cast<T*>(lt_smem);                         // [64][LDC], shared by the groups
+  T* cs0 = reinterpret_cast<T*>(lt_smem);                        // nbuf x [64][LDC], shared by the groups; with two buffers the
+                                                                 // next chunk is in flight while this one is multiplied
   const size_t group_bytes = (size_t)(LT_ROWS * LDC + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
-  T* qs = reinterpret_cast<T*>(lt_smem + (size_t)LT_KEYS * LDC * sizeof(T) + grp * group_bytes);             // [16][LDC]
+  T* qs = reinterpret_cast<T*>(lt_smem + (size_t)nbuf * LT_KEYS * LDC * sizeof(T) + grp * group_bytes);             // [16][LDC]
   T* ps = qs + LT_ROWS * LDC;                                    // [16][72]
   float* ss = reinterpret_cast<float*>(ps + LT_ROWS * 72);       // [16][68]
   float* row_m = ss + LT_ROWS * 68;                              // running max, sum, and this chunk's rescale factor
@@ -174,16 +175,29 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     jbeg = kmin + (int64_t)blockIdx.x * per * LT_KEYS;
     jend = min(plast, jbeg + per * LT_KEYS - 1);
   }
-  for (int64_t j0 = jbeg; j0 <= jend; j0 += LT_KEYS) {
-    __syncthreads();                                             // the previous chunk's products are done with cs / ss / ps
+  auto stage_chunk = [&](int64_t j0, T* dst) {                  // 64 latents from position j0 on (zero-filled past plast)
     for (int idx = threadIdx.x; idx < LT_KEYS * chunks_per_row; idx += LT_THREADS * G) {
       const int kk = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
       const bool ok = j0 + kk <= plast;
-      cp_async16((uint32_t)__cvta_generic_to_shared(cs + kk * LDC + c), ok ? (const void*)(cbase + (j0 + kk) * R + c) : (const void*)cbase, ok);
+      cp_async16((uint32_t)__cvta_generic_to_shared(dst + kk * LDC + c), ok ? (const void*)(cbase + (j0 + kk) * R + c) : (const void*)cbase, ok);
     }
     cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
+  };
+  if (nbuf > 1 && jbeg <= jend) stage_chunk(jbeg, cs0);
+  int buf = 0;
+  for (int64_t j0 = jbeg; j0 <= jend; j0 += LT_KEYS) {
+    T* cs = cs0 + (size_t)buf * LT_KEYS * LDC;
+    if (nbuf > 1) {
+      cp_async_wait<0>();
+      __syncthreads();                                           // this chunk has landed; the previous chunk's products are done
+      if (j0 + LT_KEYS <= jend) stage_chunk(j0 + LT_KEYS, cs0 + (size_t)(buf ^ 1) * LT_KEYS * LDC);
+      buf ^= 1;
+    } else {
+      __syncthreads();                                           // the previous chunk's products are done with cs / ss / ps
+      stage_chunk(j0, cs);
+      cp_async_wait<0>();
+      __syncthreads();
+    }
     if (active) {   // ---- S
       float sc[2][4];
 #pragma unroll
@@ -259,7 +273,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
   if (splits > 1) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    float* po = reinterpret_cast<float*>(cs);                    // [16][R] unnormalised partial sums (the chunk buffer is free now)
+    float* po = reinterpret_cast<float*>(cs0);                    // [16][R] unnormalised partial sums (the chunk buffer is free now)
 #pragma unroll
     for (int i = 0; i < LT_MAX_NT; ++i) {
       if (i < ntw) {
@@ -373,6 +387,7 @@ extern "C" int b200p_latent_attn(const float* q, const void* cache, int64_t Tcap
 }
 
 static int g_lt_groups = 0;     // 0: chosen per launch; 1..4: forced (b200p_latent_attn_set_groups)
+static int g_lt_nbuf = 0;       // chunk buffers of the tile kernel: 0 = chosen per launch, 1 or 2 forced (b200p_latent_attn_set_buffers)
 static int g_lt_splits = 0;     // decode: 0 = chosen per launch; 1 = one CTA per tile; 2, 4, 8 = forced (b200p_latent_attn_set_splits)
 
 template <typename T>
@@ -387,7 +402,11 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
   if (G > units) G = units;
   if (G == 3) G = 2;
   const size_t group_bytes = ((size_t)LT_ROWS * (R + 8) + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
-  const size_t smem = (size_t)LT_KEYS * (R + 8) * sizeof(T) + G * group_bytes;
+  // two chunk buffers where two CTAs per SM still fit beside them (ranks up to 256); above, the second CTA hides more latency
+  // than the second buffer (measured on prompts and on decode steps)
+  const size_t chunk_bytes = (size_t)LT_KEYS * (R + 8) * sizeof(T);
+  const int nbuf = g_lt_nbuf > 0 ? g_lt_nbuf : 2 * (2 * chunk_bytes + G * group_bytes) <= 220 * 1024 ? 2 : 1;
+  const size_t smem = nbuf * chunk_bytes + G * group_bytes;
   auto kern = G == 1 ? latent_attn_tile_kernel<T, 1> : G == 2 ? latent_attn_tile_kernel<T, 2> : latent_attn_tile_kernel<T, 4>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -417,10 +436,10 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, splits);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, splits, nbuf);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(latent_attn_tile_kernel)");
   } else {
-    kern<<<grid, LT_THREADS * G, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, 1);
+    kern<<<grid, LT_THREADS * G, smem, st>>>(q, (const T*)cache, Tcap, cu, rows, t_pos, (T*)out, H, R, window, scale, by_head, 1, nbuf);
   }
   B200P_LAUNCH_CHECK("latent_attn_tile_kernel");
   return B200P_OK;
@@ -428,6 +447,11 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
 
 extern "C" int b200p_latent_attn_set_groups(int groups) {
   g_lt_groups = groups < 0 ? 0 : groups > LT_MAX_GROUPS ? LT_MAX_GROUPS : groups;
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_attn_set_buffers(int buffers) {
+  g_lt_nbuf = buffers == 1 || buffers == 2 ? buffers : 0;
   return B200P_OK;
 }
 

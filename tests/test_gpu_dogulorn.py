@@ -479,6 +479,16 @@ def test_latent_attention_tile_kernel(R, window):
     tiles = torch.empty(M, H * R, dtype=torch.bfloat16, device="cuda")
     ops.latent_attn(qd, cd, t_row, t_pos, tiles, H, R, window, scale, cu=torch.tensor(cu, **i32), rows=torch.tensor(rows, **i32),
                     nb=5, max_n=70)
+    from mlx_parallm_b200 import _lib
+    for buffers in (1, 2):                 # one chunk buffer, or the next chunk in flight during the products: the same numbers
+        other = torch.empty_like(tiles)
+        _lib.lib().b200p_latent_attn_set_buffers(buffers)
+        try:
+            ops.latent_attn(qd, cd, t_row, t_pos, other, H, R, window, scale, cu=torch.tensor(cu, **i32), rows=torch.tensor(rows, **i32),
+                            nb=5, max_n=70)
+        finally:
+            _lib.lib().b200p_latent_attn_set_buffers(0)
+        assert torch.equal(other, tiles), buffers
     single = torch.empty_like(tiles)
     ops.latent_attn(qd, cd, t_row, t_pos, single, H, R, window, scale)
     want = torch.zeros(M, H, R, dtype=torch.float64)
