@@ -269,8 +269,10 @@ int b200p_peer_status(const void* flags_local, uint32_t* host_out, void* stream)
 enum {
   B200P_GEMM_STORE = 0,      /* y[M,N] (dtype) = acc                                                             */
   B200P_GEMM_STORE_F32 = 1,  /* y[M,N] (float) = acc                                                             */
-  B200P_GEMM_GLU_CLAMP = 2   /* rows 2i / 2i+1 of w are gate_i / up_i: y[M,N/2] (dtype) = g * sigmoid(1.702 g) * (u + 1),
+  B200P_GEMM_GLU_CLAMP = 2,  /* rows 2i / 2i+1 of w are gate_i / up_i: y[M,N/2] (dtype) = g * sigmoid(1.702 g) * (u + 1),
                                 g = min(gate, limit), u = clamp(up, -limit, limit)                                  */
+  B200P_GEMM_GLU_GELU_TANH = 3, /* same row pairs: y = gelu_tanh(gate) * up                                          */
+  B200P_GEMM_GLU_SILU = 4    /* same row pairs: y = gate * sigmoid(gate) * up                                       */
 };
 /* y = x . w^T, x [M,K] and w [N,K] in `dtype` (row strides ldx / ldw elements), fp32 accumulation; `batch` independent
  * products at element strides stride_x / stride_w / stride_y.  B200P_F32 runs true fp32 FMAs in ascending k.  16-bit calls
@@ -279,6 +281,13 @@ enum {
 int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
                int64_t batch, int64_t stride_x, int64_t stride_w, int64_t stride_y, int dtype, int epilogue, float limit,
                void* stream);
+
+/* Grouped product (the experts of a mixture): group z < groups multiplies the rows [seg[z], seg[z+1]) of x (and writes the same
+ * rows of y) by its own weight block w + z * stride_w ([N, K]); seg is a DEVICE array of groups + 1 ascending offsets and
+ * max_rows an upper bound of a group's row count, which sizes the launch (so the launch does not depend on the routing). */
+int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+                       int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t stride_w, int dtype, int epilogue,
+                       float limit, void* stream);
 
 /* 0 (default): calls of 9 rows and more run on tcgen05 (TMA-fed shared-memory operands, TMEM accumulators; up to 64 rows with the
  * weights on the MMA's M side and K split where the output is narrow, which adds fp32 partial sums in no fixed order) and fall
@@ -307,32 +316,79 @@ int b200p_embed_hashed(const int32_t* ids, const int32_t* t_row, const int32_t* 
  * rows [M, W]; weights fp32. */
 int b200p_norm_add_norm(const float* y, const float* w_post, float* h, const float* w_next, void* x_out, void* raw_out,
                         int64_t M, int64_t W, float eps, int dtype, void* stream);
+/* Residual stream of designs that add their sublayers without a norm of their own, one pass per row:
+ *   h += c1 * y1 + c2 * y2 (either may be NULL);  raw_out (rows of stride ld_raw) = h in `dtype`;
+ *   x_out = h / sqrt(mean(h^2) + eps) * w_next in `dtype`.  rows [M, W]; h, y, weights fp32. */
+int b200p_residual_add_norm(float* h, const float* y1, float c1, const float* y2, float c2, const float* w_next, void* x_out,
+                            void* raw_out, int64_t ld_raw, int64_t M, int64_t W, float eps, int dtype, void* stream);
+/* dst[t, c] (dtype, row stride ld_dst) = src[t, c] (fp32, row stride ld_src), c < n */
+int b200p_cast_columns(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t M, int64_t n, int dtype, void* stream);
 /* out[t, c] (dtype) = gelu_tanh(gate[t, c]) * table[ids[t], col0 + c], c < d; gate fp32 [M, d], table [*, ld_table] `dtype` */
 int b200p_token_gate(const float* gate, const void* table, const int32_t* ids, void* out, int64_t M, int d, int64_t ld_table,
                      int64_t col0, int dtype, void* stream);
 
-/* Gated delta rule, step 1.  proj fp32 [M, ldp] holds the fused projection [q | k | v | gate | b | a]: q, k (KH heads x dk) and
- * v (H heads x dv) are columns [0, C), C = 2 KH dk + H dv.  Per channel a causal convolution of `taps` taps (conv_w [C, taps],
+/* Gated delta rule, step 1.  proj fp32 [M, ldp] holds the fused projection [q | k | v | ...]: q, k (KH heads x dk) and
+ * v (H heads x dv) are columns [0, C), C = 2 KH dk + H dv; b (H columns) starts at col_b; the decay's step input is `a`
+ * (fp32, row stride lda: a slice of proj or a tensor of its own) with decay_per_head values per head: 1 (one decay for the
+ * head's whole state) or dk (one per key channel, i.e. per row of the state).  Per channel a causal convolution of `taps` taps (conv_w [C, taps],
  * last column = current token; inputs before position 0 are zero, inputs before the portion come from conv_state
  * [rows, taps-1, C]) then silu; q and k are made unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q times dk^-1/2;
- * beta = sigmoid(b); decay = exp(-exp(A_log) * softplus(a + dt_bias)).  Outputs fp32: qn, kn [M, KH dk], v [M, H dv],
- * beta, decay [M, H]. */
-int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* conv_w, const float* conv_state,
+ * beta = sigmoid(b); decay = exp(-exp(A_log[head]) * softplus(a + dt_bias)), dt_bias one per decay.  Outputs fp32: qn, kn
+ * [M, KH dk], v [M, H dv], beta [M, H], decay [M, H * decay_per_head]. */
+int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, const float* a, int64_t lda, int decay_per_head,
+                     const float* conv_w, const float* conv_state,
                      const float* A_log, const float* dt_bias, const int32_t* t_row, const int32_t* t_pos, const int32_t* t_off,
                      float* qn, float* kn, float* v, float* beta, float* decay, int64_t M, int H, int KH, int dk, int dv,
                      int taps, void* stream);
 /* step 2 (after b200p_delta_prep of the same step): conv_state of every entry's row takes the last taps-1 inputs */
 int b200p_delta_conv_commit(const float* proj, int64_t ldp, float* conv_state, const int32_t* cu, const int32_t* rows, int nb,
                             int64_t C, int taps, void* stream);
-/* step 3: per entry and head, token by token in fp32: S *= decay; u = beta (v - S^T k); S += k u^T; o = S^T q.
+/* b200p_delta_scan modes */
+enum {
+  B200P_SCAN_DELTA = 0,          /* decay [M, H]:      S *= g;          u = beta (v - S^T k); S += k u^T; o = S^T q */
+  B200P_SCAN_DELTA_CHANNEL = 1,  /* decay [M, H, dk]:  S = diag(g) S;   then the same                                */
+  B200P_SCAN_ACCUMULATE = 2      /* decay [M, H]:      S = g S + k v^T; o = S^T q   (beta may be NULL)               */
+};
+/* step 3: per entry and head, token by token in fp32, by `mode`.
  * state [rows, H, dk, dv] fp32 is read (zero when the entry starts at position 0) and written back; head h reads q/k head
  * h / (H / KH).  o fp32 [M, H dv]. */
 int b200p_delta_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay, float* state,
                      const int32_t* cu, const int32_t* rows, const int32_t* lengths, float* o, int nb, int H, int KH, int dk,
-                     int dv, void* stream);
-/* step 4: out[t, h, :] (dtype) = o / sqrt(mean_dv(o^2) + eps) * norm_w * silu(gate[t, h, :]); gate = proj columns col_g.. */
-int b200p_delta_out(const float* o, const float* proj, int64_t ldp, int64_t col_g, const float* norm_w, void* out, int64_t M,
-                    int H, int dv, float eps, int dtype, void* stream);
+                     int dv, int mode, void* stream);
+/* step 4: out[t, h, :] (dtype, row stride ld_out) = out_scale * o / sqrt(mean_dv(o^2) + eps) * norm_w * act(gate[t, h, :]);
+ * gate fp32 with row stride ldg; gate_act 0 silu, 1 sigmoid.  H == 1 norms the dv values of a row as one group. */
+int b200p_delta_out(const float* o, const float* gate, int64_t ldg, const float* norm_w, void* out, int64_t ld_out, int64_t M,
+                    int H, int dv, float eps, int gate_act, float out_scale, int dtype, void* stream);
+/* Inputs of the plain decayed accumulation (B200P_SCAN_ACCUMULATE): proj fp32 [M, ldp] = [q | k (H x dk each) | v (H x dv)];
+ * q, k, v = silu of them (fp32); decay[t, h] = head_decay[h]. */
+int b200p_linear_attn_prep(const float* proj, int64_t ldp, const float* head_decay, float* q, float* k, float* v, float* decay,
+                           int64_t M, int H, int dk, int dv, void* stream);
+
+/* Attention without a rotation, with grouped heads, a distance bias and a sink.  Step 1: proj fp32 [M, ldp] holds q (H x dk) at
+ * col_q, k (G x dk) at col_k, v (G x dv) at col_v.  q_out fp32 [M, H dk] = rms_norm(q) * wq * scale * temperature, temperature
+ * = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) at position p; rms_norm(k) * wk and v go to the caches
+ * [rows, G, Tcap, dk] / [rows, G, Tcap, dv] (dtype) at (t_row, t_pos).  wq / wk NULL: no norm. */
+int b200p_sink_attn_prep(const float* proj, int64_t ldp, int64_t col_q, int64_t col_k, int64_t col_v, const float* wq,
+                         const float* wk, float eps, float scale, float temp_coef, float temp_every, float* q_out, void* kcache,
+                         void* vcache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, int64_t M, int H, int G, int dk,
+                         int dv, int dtype, void* stream);
+/* step 2: token t at position p of row r sees j <= p; score_j = q . k_j - slope_h (p - j), slope_h = 2^(slope_log2 (h+1) / H)
+ * (slope_log2 == 0: no bias); fp32 softmax whose denominator also holds exp(sink[h]) (sink NULL: none);
+ * out[t, h, :] (dtype, row stride ld_out) = out_scale * sum_j p_j v_j.  Query head h reads key/value head h / (H / G). */
+int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
+                    const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
+                    int64_t M, int H, int G, int dk, int dv, int dtype, void* stream);
+
+/* Routed experts.  logits fp32 [M, ldl] (+ bias [E] or NULL): ids / wts [M, top] = the `top` largest and the softmax over those;
+ * seg [E + 1] = offsets of every expert's rows among the M * top slots; slot_of [M * top] the slot of choice k of token t;
+ * token_of [M * top] the token of a slot. */
+int b200p_moe_route(const float* logits, int64_t ldl, const float* bias, int32_t* ids, float* wts, int32_t* seg, int32_t* slot_of,
+                    int32_t* token_of, int64_t M, int E, int top, void* stream);
+/* xs[s, :] = x[token_of[s], :], rows of W elements in `dtype` */
+int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs, int64_t slots, int64_t W, int dtype, void* stream);
+/* y[t, :] = (shared_y ? shared_y[t, :] : 0) + sum_k wts[t, k] * ye[slot_of[t, k], :], all fp32 */
+int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y, float* y, int64_t M,
+                      int64_t W, int top, void* stream);
 
 /* Latent attention, step 1.  proj fp32 [M, ldp] = [down-projected query (q_rank) | down-projected key/value (kv_rank)].
  * cq_out [M, q_rank] (dtype) = rms_norm(query part) * wq; the key/value part, rms_norm * wkv, is written to

@@ -72,11 +72,21 @@ SIGNATURES = {
     "b200p_embed_hashed": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i64, _i64, _i64, _i32, _vp]),
     "b200p_norm_add_norm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _vp]),
     "b200p_token_gate": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _vp]),
-    "b200p_delta_prep": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+    "b200p_delta_prep": (_i32, [_vp, _i64, _i64, _vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                 _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200p_delta_conv_commit": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp]),
-    "b200p_delta_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
-    "b200p_delta_out": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _f32, _i32, _vp]),
+    "b200p_delta_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200p_delta_out": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _i32, _f32, _i32, _vp]),
+    "b200p_linear_attn_prep": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
+    "b200p_gemm_grouped": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
+    "b200p_residual_add_norm": (_i32, [_vp, _vp, _f32, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
+    "b200p_cast_columns": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "b200p_sink_attn_prep": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _f32, _f32, _f32, _f32, _vp, _vp, _vp, _i64, _vp, _vp,
+                                    _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200p_sink_attn": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _f32, _vp, _i64, _f32, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200p_moe_route": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b200p_moe_gather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "b200p_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp]),
     "b200p_latent_prep": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp]),
     "b200p_latent_attn": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _f32, _i32, _vp]),
     "b200p_latent_attn_set_groups": (_i32, [_i32]),
@@ -90,8 +100,11 @@ SIGNATURES = {
 # that serves one design compiles that design's kernels only.  ``None`` = every unit (libb200parallm.so).
 UNIT_SETS = {
     "sequence": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "latent_attn", "sampler"),
+    "sequence_moe": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "sink_attn", "moe", "sampler"),
 }
-GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP = 0, 1, 2
+GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU = 0, 1, 2, 3, 4
+SCAN_DELTA, SCAN_DELTA_CHANNEL, SCAN_ACCUMULATE = 0, 1, 2
+GATE_SILU, GATE_SIGMOID = 0, 1
 
 _lib = None
 

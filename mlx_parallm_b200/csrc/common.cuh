@@ -68,6 +68,21 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- gated hidden unit of a feed-forward, computed in the GEMM epilogue from the (gate, up) pair of one unit --------------
+__device__ __forceinline__ float gelu_tanh_unit(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ bool gemm_epi_is_glu(int epi) { return epi >= B200P_GEMM_GLU_CLAMP; }
+__device__ __forceinline__ float glu_unit(float gate, float up, int epi, float limit) {
+  if (epi == B200P_GEMM_GLU_CLAMP) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
+  }
+  if (epi == B200P_GEMM_GLU_GELU_TANH) return gelu_tanh_unit(gate) * up;
+  return gate / (1.f + expf(-gate)) * up;                          // B200P_GEMM_GLU_SILU
+}
+
 // streaming 128-bit load that does not pollute L1 (weights / KV are read once)
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 r;

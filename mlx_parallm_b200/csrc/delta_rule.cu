@@ -4,6 +4,9 @@
 //   delta_conv_commit_kernel  the convolution's carried inputs                                                   (per entry)
 //   delta_scan_kernel         the recurrence, fp32, token by token; four lanes per pair of state columns           (per entry, head)
 //   delta_out_kernel          per-head rms norm * weight * silu(gate)                                            (per token)
+// The same kernels carry the variants other designs use: a decay per head AND key channel (a row of S each), a gate that is a
+// sigmoid of a separate tensor, and the plain decayed accumulation S <- g S + k v^T (linear attention with a constant decay,
+// fed by linear_attn_prep_kernel).
 // Prompts and single decoded tokens run the SAME scan kernel in the same summation order, so a prompt cut into portions gives
 // the same numbers as one pass.
 #include "common.cuh"
@@ -17,7 +20,8 @@ constexpr int DELTA_MAX_TAPS = 16;
 
 template <int NT>
 __global__ void __launch_bounds__(NT)
-delta_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* __restrict__ conv_w,
+delta_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_b, const float* __restrict__ a, int64_t lda, int dper,
+                  const float* __restrict__ conv_w,
                   const float* __restrict__ conv_state, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                   const int32_t* __restrict__ t_row, const int32_t* __restrict__ t_pos, const int32_t* __restrict__ t_off,
                   float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vout, float* __restrict__ beta,
@@ -54,10 +58,28 @@ delta_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_b, in
     else dst = kn + t * (int64_t)(KH * dk) + (hd - KH) * dk;
     for (int i = lane; i < dk; i += 32) dst[i] = src[i] * inv;
   }
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    beta[t * H + h] = 1.f / (1.f + expf(-pt[col_b + h]));
-    decay[t * H + h] = expf(-expf(A_log[h]) * softplus_f(pt[col_a + h] + dt_bias[h]));
+  for (int h = threadIdx.x; h < H; h += blockDim.x) beta[t * H + h] = 1.f / (1.f + expf(-pt[col_b + h]));
+  // dper decays per head (1: the whole state of a head; dk: one per key channel), each with its own step input and bias
+  const int nd = H * dper;
+  const float* at = a + t * lda;
+  for (int i = threadIdx.x; i < nd; i += blockDim.x)
+    decay[t * (int64_t)nd + i] = expf(-expf(A_log[i / dper]) * softplus_f(at[i] + dt_bias[i]));
+}
+
+// Inputs of the plain decayed accumulation: q, k, v = silu of their projections (columns [0, Cqk), [Cqk, 2 Cqk), [2 Cqk, ..) of
+// proj), and the constant per-head decay repeated for every token so that the scan reads it like a computed one.
+__global__ void linear_attn_prep_kernel(const float* __restrict__ proj, int64_t ldp, const float* __restrict__ head_decay,
+                                        float* __restrict__ q, float* __restrict__ k, float* __restrict__ v,
+                                        float* __restrict__ decay, int H, int Cqk, int Cv) {
+  const int64_t t = blockIdx.x;
+  const float* pt = proj + t * ldp;
+  for (int c = threadIdx.x; c < 2 * Cqk + Cv; c += blockDim.x) {
+    const float a = silu_f(pt[c]);
+    if (c < Cqk) q[t * Cqk + c] = a;
+    else if (c < 2 * Cqk) k[t * Cqk + (c - Cqk)] = a;
+    else v[t * (int64_t)Cv + (c - 2 * Cqk)] = a;
   }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) decay[t * H + h] = head_decay[h];
 }
 
 __global__ void delta_conv_commit_kernel(const float* __restrict__ proj, int64_t ldp, float* __restrict__ conv_state,
@@ -91,7 +113,9 @@ constexpr int ds_cols(int dkp) { return 2 * DS_THREADS / ds_lanes(dkp); }      /
 // packed fp32 instructions of sm_100 (FMUL2 / FFMA2: both halves rounded like the scalar operation) update both columns at
 // once.  Each reduction over dk is as much shorter plus log2(lanes) exchanges between the lanes.  q and k of CHUNK tokens are
 // staged in shared memory with every lane's part padded by 16 bytes, so the lanes' 128-bit reads fall into different banks.
-template <int DKP>
+// MODE 0: delta rule, one decay per head and token; 1: delta rule, one decay per head, key channel and token (decay
+// [M, H, dk]); 2: no correction, S <- g S + k v^T (one decay per head and token; beta unused).
+template <int DKP, int MODE>
 __global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
@@ -104,6 +128,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   constexpr int PF = CHUNK * DKP / DS_THREADS;                   // q / k elements each thread stages per chunk
   constexpr int PV = (CHUNK * DS_COLS + DS_THREADS - 1) / DS_THREADS;
   __shared__ __align__(16) float ks[2][CHUNK][LDK], qs[2][CHUNK][LDK];
+  __shared__ __align__(16) float gc[MODE == 1 ? 2 : 1][MODE == 1 ? CHUNK : 1][MODE == 1 ? LDK : 4];     // per-channel decays
   __shared__ float vs[2][CHUNK][DS_COLS], gs[2][CHUNK], bs[2][CHUNK];
   const int e = blockIdx.x, h = blockIdx.y;
   const int l = threadIdx.x & (DS_LANES - 1), slot = threadIdx.x / DS_LANES;
@@ -125,6 +150,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   // The next chunk's inputs are fetched into registers while the current chunk runs out of shared memory, then parked in the
   // other buffer: the recurrence never waits for global memory.
   float pk[PF], pq[PF], pv[PV], pg = 0.f, pb = 0.f;
+  float pgc[MODE == 1 ? PF : 1];
   auto fetch = [&](int tc) {
     const int nt = min(CHUNK, t1 - tc);
 #pragma unroll
@@ -134,6 +160,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       const int64_t src = ((int64_t)(tc + tt) * KH + kh) * dk + i;
       pk[r] = ok ? kn[src] : 0.f;
       pq[r] = ok ? qn[src] : 0.f;
+      if constexpr (MODE == 1) pgc[r] = ok ? decay[((int64_t)(tc + tt) * H + h) * dk + i] : 1.f;
     }
 #pragma unroll
     for (int r = 0; r < PV; ++r) {
@@ -141,8 +168,8 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       pv[r] = (tt < nt && c < dv) ? v[((int64_t)(tc + tt) * H + h) * dv + c] : 0.f;
     }
     if (threadIdx.x < nt) {
-      pg = decay[(int64_t)(tc + threadIdx.x) * H + h];
-      pb = beta[(int64_t)(tc + threadIdx.x) * H + h];
+      if constexpr (MODE != 1) pg = decay[(int64_t)(tc + threadIdx.x) * H + h];
+      if constexpr (MODE != 2) pb = beta[(int64_t)(tc + threadIdx.x) * H + h];
     }
   };
   auto park = [&](int buf) {
@@ -151,6 +178,7 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       const int idx = threadIdx.x + r * DS_THREADS, tt = idx / DKP, i = idx % DKP;
       ks[buf][tt][i + (i / SEG) * 4] = pk[r];
       qs[buf][tt][i + (i / SEG) * 4] = pq[r];
+      if constexpr (MODE == 1) gc[buf][tt][i + (i / SEG) * 4] = pgc[r];
     }
 #pragma unroll
     for (int r = 0; r < PV; ++r) {
@@ -184,19 +212,27 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
       for (int i = 0; i < SEG; i += 4) {
         const float4 k4 = kr[i / 4] = *reinterpret_cast<const float4*>(kp + i);
         const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+        float gg[4] = {g, g, g, g};
+        if constexpr (MODE == 1) {
+          const float4 g4 = *reinterpret_cast<const float4*>(&gc[buf][tt][l * (SEG + 4) + i]);
+          gg[0] = g4.x, gg[1] = g4.y, gg[2] = g4.z, gg[3] = g4.w;
+        }
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
-          S2[i + a] = __fmul2_rn(S2[i + a], g2);
-          d[a] = __ffma2_rn(S2[i + a], make_float2(kk[a], kk[a]), d[a]);
+          S2[i + a] = __fmul2_rn(S2[i + a], MODE == 1 ? make_float2(gg[a], gg[a]) : g2);
+          if constexpr (MODE != 2) d[a] = __ffma2_rn(S2[i + a], make_float2(kk[a], kk[a]), d[a]);
         }
       }
-      float dx = (d[0].x + d[1].x) + (d[2].x + d[3].x), dy = (d[0].y + d[1].y) + (d[2].y + d[3].y);
+      float2 u2 = v2;
+      if constexpr (MODE != 2) {
+        float dx = (d[0].x + d[1].x) + (d[2].x + d[3].x), dy = (d[0].y + d[1].y) + (d[2].y + d[3].y);
 #pragma unroll
-      for (int m = 1; m < DS_LANES; m <<= 1) {
-        dx += __shfl_xor_sync(0xffffffffu, dx, m);
-        dy += __shfl_xor_sync(0xffffffffu, dy, m);
+        for (int m = 1; m < DS_LANES; m <<= 1) {
+          dx += __shfl_xor_sync(0xffffffffu, dx, m);
+          dy += __shfl_xor_sync(0xffffffffu, dy, m);
+        }
+        u2 = make_float2(b * (v2.x - dx), b * (v2.y - dy));
       }
-      const float2 u2 = make_float2(b * (v2.x - dx), b * (v2.y - dy));
       float2 oa[4];
 #pragma unroll
       for (int a = 0; a < 4; ++a) oa[a] = make_float2(0.f, 0.f);
@@ -235,19 +271,41 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
   }
 }
 
+__device__ __forceinline__ float gate_act_f(float z, int act) { return act == 0 ? silu_f(z) : 1.f / (1.f + expf(-z)); }
+
+// groups of dv values (a head each, or all heads as one group when H == 1) are rms-normed, weighted by norm_w [dv], gated by
+// act(gate) (0 silu, 1 sigmoid) and scaled; out rows have stride ld_out
 template <typename T>
-__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, int64_t ldp, int64_t col_g,
-                                 const float* __restrict__ norm_w, T* __restrict__ out, int H, int dv, float eps) {
+__global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t ldg,
+                                 const float* __restrict__ norm_w, T* __restrict__ out, int64_t ld_out, int H, int dv, float eps,
+                                 int act, float out_scale) {
   const int64_t t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (H == 1) {                                   // one wide group: the whole block sums it, in an order fixed by the block size
+    __shared__ float red[32];
+    const float* src = o + t * dv;
+    const float* g = gate + t * ldg;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    const float inv = out_scale / sqrtf(tot / (float)dv + eps);
+    for (int i = threadIdx.x; i < dv; i += blockDim.x)
+      out[t * ld_out + i] = Tr<T>::from_f(src[i] * inv * norm_w[i] * gate_act_f(g[i], act));
+    return;
+  }
   for (int h = warp; h < H; h += nw) {
     const float* src = o + (t * H + h) * dv;
-    const float* g = proj + t * ldp + col_g + (int64_t)h * dv;
+    const float* g = gate + t * ldg + (int64_t)h * dv;
     float ss = 0.f;
     for (int i = lane; i < dv; i += 32) ss = fmaf(src[i], src[i], ss);
     ss = warp_sum(ss);
-    const float inv = 1.f / sqrtf(ss / (float)dv + eps);
-    for (int i = lane; i < dv; i += 32) out[(t * H + h) * dv + i] = Tr<T>::from_f(src[i] * inv * norm_w[i] * silu_f(g[i]));
+    const float inv = out_scale / sqrtf(ss / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32)
+      out[t * ld_out + (int64_t)h * dv + i] = Tr<T>::from_f(src[i] * inv * norm_w[i] * gate_act_f(g[i], act));
   }
 }
 
@@ -255,10 +313,11 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
 
 using namespace b200p;
 
-extern "C" int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, int64_t col_a, const float* conv_w,
-                                const float* conv_state, const float* A_log, const float* dt_bias, const int32_t* t_row,
+extern "C" int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, const float* a, int64_t lda, int decay_per_head,
+                                const float* conv_w, const float* conv_state, const float* A_log, const float* dt_bias, const int32_t* t_row,
                                 const int32_t* t_pos, const int32_t* t_off, float* qn, float* kn, float* v, float* beta,
                                 float* decay, int64_t M, int H, int KH, int dk, int dv, int taps, void* stream) {
+  B200P_REQUIRE(a && (decay_per_head == 1 || decay_per_head == dk), B200P_ERR_ARG, "one decay per head, or one per key channel");
   B200P_REQUIRE(proj && conv_w && conv_state && A_log && dt_bias && t_row && t_pos && t_off && qn && kn && v && beta && decay,
                 B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(H > 0 && KH > 0 && H % KH == 0 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
@@ -268,10 +327,10 @@ extern "C" int b200p_delta_prep(const float* proj, int64_t ldp, int64_t col_b, i
   B200P_REQUIRE(smem <= 48 * 1024, B200P_ERR_ARG, "q and k of one token must fit 48 KB of shared memory");
   // a decode batch has few tokens and thousands of channels each: wider blocks shorten the per-thread channel loop
   if (M <= 256)
-    delta_prep_kernel<1024><<<(unsigned)M, 1024, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row,
+    delta_prep_kernel<1024><<<(unsigned)M, 1024, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, a, lda, decay_per_head, conv_w, conv_state, A_log, dt_bias, t_row,
                                                                                t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps);
   else
-    delta_prep_kernel<256><<<(unsigned)M, 256, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row,
+    delta_prep_kernel<256><<<(unsigned)M, 256, smem, (cudaStream_t)stream>>>(proj, ldp, col_b, a, lda, decay_per_head, conv_w, conv_state, A_log, dt_bias, t_row,
                                                                              t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps);
   B200P_LAUNCH_CHECK("delta_prep_kernel");
   return B200P_OK;
@@ -288,32 +347,54 @@ extern "C" int b200p_delta_conv_commit(const float* proj, int64_t ldp, float* co
   return B200P_OK;
 }
 
+template <int MODE>
+static void delta_scan_launch(dim3 grid, cudaStream_t st, const float* qn, const float* kn, const float* v, const float* beta,
+                              const float* decay, float* state, const int32_t* cu, const int32_t* rows, const int32_t* lengths,
+                              float* o, int H, int KH, int dk, int dv) {
+  const int threads = DS_THREADS;
+  if (dk <= 32) delta_scan_kernel<32, MODE><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 64) delta_scan_kernel<64, MODE><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 128) delta_scan_kernel<128, MODE><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (dk <= 256) delta_scan_kernel<256, MODE><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else delta_scan_kernel<512, MODE><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+}
+
 extern "C" int b200p_delta_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay,
                                 float* state, const int32_t* cu, const int32_t* rows, const int32_t* lengths, float* o, int nb,
-                                int H, int KH, int dk, int dv, void* stream) {
-  B200P_REQUIRE(qn && kn && v && beta && decay && state && cu && rows && lengths && o, B200P_ERR_ARG, "null pointer");
+                                int H, int KH, int dk, int dv, int mode, void* stream) {
+  B200P_REQUIRE(qn && kn && v && decay && state && cu && rows && lengths && o, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(mode >= B200P_SCAN_DELTA && mode <= B200P_SCAN_ACCUMULATE, B200P_ERR_ARG, "unknown scan mode %d", mode);
+  B200P_REQUIRE(beta || mode == B200P_SCAN_ACCUMULATE, B200P_ERR_ARG, "the delta rule needs beta");
   B200P_REQUIRE(nb > 0 && H > 0 && KH > 0 && H % KH == 0 && H < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dk <= 512, B200P_ERR_ARG, "key size %d > 512 is not built", dk);
-  const int threads = DS_THREADS;
   const int dkp = dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : dk <= 256 ? 256 : 512, cols = ds_cols(dkp);
   dim3 grid((unsigned)nb, (unsigned)H, (unsigned)((dv + cols - 1) / cols));
   cudaStream_t st = (cudaStream_t)stream;
-  if (dk <= 32) delta_scan_kernel<32><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
-  else if (dk <= 64) delta_scan_kernel<64><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
-  else if (dk <= 128) delta_scan_kernel<128><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
-  else if (dk <= 256) delta_scan_kernel<256><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
-  else delta_scan_kernel<512><<<grid, threads, 0, st>>>(qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  if (mode == B200P_SCAN_DELTA) delta_scan_launch<0>(grid, st, qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else if (mode == B200P_SCAN_DELTA_CHANNEL) delta_scan_launch<1>(grid, st, qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
+  else delta_scan_launch<2>(grid, st, qn, kn, v, beta, decay, state, cu, rows, lengths, o, H, KH, dk, dv);
   B200P_LAUNCH_CHECK("delta_scan_kernel");
   return B200P_OK;
 }
 
-extern "C" int b200p_delta_out(const float* o, const float* proj, int64_t ldp, int64_t col_g, const float* norm_w, void* out,
-                               int64_t M, int H, int dv, float eps, int dtype, void* stream) {
-  B200P_REQUIRE(o && proj && norm_w && out && H > 0 && dv > 0, B200P_ERR_ARG, "null pointer");
+extern "C" int b200p_linear_attn_prep(const float* proj, int64_t ldp, const float* head_decay, float* q, float* k, float* v,
+                                      float* decay, int64_t M, int H, int dk, int dv, void* stream) {
+  B200P_REQUIRE(proj && head_decay && q && k && v && decay && H > 0 && dk > 0 && dv > 0, B200P_ERR_ARG, "null pointer");
   if (M == 0) return B200P_OK;
-  const unsigned threads = H >= 8 ? 256 : 32 * (unsigned)H;
+  linear_attn_prep_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(proj, ldp, head_decay, q, k, v, decay, H, H * dk, H * dv);
+  B200P_LAUNCH_CHECK("linear_attn_prep_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_delta_out(const float* o, const float* gate, int64_t ldg, const float* norm_w, void* out, int64_t ld_out,
+                               int64_t M, int H, int dv, float eps, int gate_act, float out_scale, int dtype, void* stream) {
+  B200P_REQUIRE(o && gate && norm_w && out && H > 0 && dv > 0, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(gate_act == 0 || gate_act == 1, B200P_ERR_ARG, "gate activation: 0 silu, 1 sigmoid");
+  B200P_REQUIRE(ld_out >= (int64_t)H * dv, B200P_ERR_ARG, "output rows are shorter than the heads");
+  if (M == 0) return B200P_OK;
+  const unsigned threads = H == 1 ? (dv >= 1024 ? 256 : 128) : H >= 8 ? 256 : 32 * (unsigned)H;
   B200P_DISPATCH_DTYPE(dtype, T, (delta_out_kernel<T><<<(unsigned)M, threads, 0, (cudaStream_t)stream>>>(
-      o, proj, ldp, col_g, norm_w, (T*)out, H, dv, eps)));
+      o, gate, ldg, norm_w, (T*)out, ld_out, H, dv, eps, gate_act, out_scale)));
   B200P_LAUNCH_CHECK("delta_out_kernel");
   return B200P_OK;
 }

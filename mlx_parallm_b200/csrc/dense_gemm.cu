@@ -34,15 +34,25 @@ __device__ __forceinline__ void gemm_store_pair(void* y, int64_t row_off, int64_
     T* p = reinterpret_cast<T*>(y) + row_off;
     if (n < N) p[n] = Tr<T>::from_f(v0);
     if (n + 1 < N) p[n + 1] = Tr<T>::from_f(v1);
-  } else {  // B200P_GEMM_GLU_CLAMP: v0 = gate, v1 = up of hidden unit n / 2
-    if (n + 1 < N) {
-      const float g = fminf(v0, limit);
-      const float u = fminf(fmaxf(v1, -limit), limit);
-      const float a = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
-      reinterpret_cast<T*>(y)[row_off + (n >> 1)] = Tr<T>::from_f(a);
-    }
+  } else {  // gated units: v0 = gate, v1 = up of hidden unit n / 2
+    if (n + 1 < N) reinterpret_cast<T*>(y)[row_off + (n >> 1)] = Tr<T>::from_f(glu_unit(v0, v1, epi, limit));
   }
 }
+
+// Grouped calls (a mixture of experts: group z owns the rows [seg[z], seg[z+1]) of x and y and the z-th weight block): the row
+// count and the row offsets of a CTA's product come from the device array instead of the launch, so the launch is the same
+// whatever the routing (and can sit in a captured graph).  Without `seg` the products are `batch` equal ones at fixed strides.
+#define GEMM_GROUP_ROWS(seg, z, M, x, ldx, sx, ybase, ldy, sy) \
+  int64_t ybase;                                                \
+  if (seg) {                                                    \
+    const int64_t s0__ = seg[z];                                \
+    M = seg[z + 1] - s0__;                                      \
+    x += s0__ * ldx;                                            \
+    ybase = s0__ * ldy;                                         \
+  } else {                                                      \
+    x += z * sx;                                                \
+    ybase = z * sy;                                             \
+  }
 
 // ---- generic kernel ---------------------------------------------------------------------------------------------------
 constexpr int GS_BM = 64, GS_BN = 64, GS_BK = 16;
@@ -50,13 +60,15 @@ constexpr int GS_BM = 64, GS_BN = 64, GS_BK = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int64_t M, int64_t N, int64_t K,
-                 int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+                 int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit,
+                 const int32_t* __restrict__ seg) {
   __shared__ float xs[GS_BK][GS_BM + 4];
   __shared__ float ws[GS_BK][GS_BN + 4];
   const int64_t z = blockIdx.z;
-  x += z * sx;
+  GEMM_GROUP_ROWS(seg, z, M, x, ldx, sx, ybase, ldy, sy);
   w += z * sw;
   const int64_t m0 = (int64_t)blockIdx.y * GS_BM, n0 = (int64_t)blockIdx.x * GS_BN;
+  if (m0 >= M) return;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // 4 x 4 outputs: rows ty*4.., columns tx*4..
   float acc[4][4];
 #pragma unroll
@@ -88,7 +100,7 @@ gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restr
   for (int i = 0; i < 4; ++i) {
     const int64_t m = m0 + ty * 4 + i;
     if (m >= M) continue;
-    const int64_t off = z * sy + m * ldy;
+    const int64_t off = ybase + m * ldy;
 #pragma unroll
     for (int j = 0; j < 4; j += 2) gemm_store_pair<T>(y, off, n0 + tx * 4 + j, N, acc[i][j], acc[i][j + 1], epi, limit);
   }
@@ -103,16 +115,18 @@ constexpr int GM_PAD = 8;
 template <typename T, int WM, int WN, int WTM, int WTN, int BK, int STAGES>
 __global__ void __launch_bounds__(WM * WN * 32)
 gemm_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int64_t M, int64_t N, int64_t K,
-                int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+                int64_t ldx, int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit,
+                const int32_t* __restrict__ seg) {
   constexpr int BM = WM * WTM, BN = WN * WTN, NT = WM * WN * 32, LDS = BK + GM_PAD, MI = WTM / 16, NJ = WTN / 8;
   static_assert(WTM % 16 == 0 && WTN % 16 == 0 && BK % 16 == 0, "warp blocks are made of 16 x 16 pieces");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);                       // [STAGES][BM][LDS]
   T* ws = xs + STAGES * BM * LDS;                               // [STAGES][BN][LDS]
   const int64_t z = blockIdx.z;
-  x += z * sx;
+  GEMM_GROUP_ROWS(seg, z, M, x, ldx, sx, ybase, ldy, sy);
   w += z * sw;
   const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+  if (m0 >= M) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wm = warp / WN, wn = warp % WN;
   const int nk = (int)((K + BK - 1) / BK);
@@ -176,7 +190,7 @@ gemm_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restri
     for (int hf = 0; hf < 2; ++hf) {
       const int64_t m = m0 + wm * WTM + i * 16 + (lane >> 2) + hf * 8;
       if (m >= M) continue;
-      const int64_t off = z * sy + m * ldy;
+      const int64_t off = ybase + m * ldy;
 #pragma unroll
       for (int j = 0; j < NJ; ++j)
         gemm_store_pair<T>(y, off, n0 + wn * WTN + j * 8 + (lane & 3) * 2, N, acc[i][j][hf * 2], acc[i][j][hf * 2 + 1], epi, limit);
@@ -185,7 +199,8 @@ gemm_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restri
 
 template <typename T, int WM, int WN, int WTM, int WTN, int BK, int STAGES>
 static int gemm_mma_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
-                           int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st) {
+                           int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st,
+                           const int32_t* seg = nullptr) {
   constexpr int BM = WM * WTM, BN = WN * WTN;
   constexpr size_t smem = (size_t)STAGES * (BM + BN) * (BK + GM_PAD) * sizeof(T);
   auto kern = gemm_mma_kernel<T, WM, WN, WTM, WTN, BK, STAGES>;
@@ -198,7 +213,7 @@ static int gemm_mma_launch(const T* x, const T* w, void* y, int64_t M, int64_t N
     }
   }
   dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + BM - 1) / BM), (unsigned)batch);
-  kern<<<grid, WM * WN * 32, smem, st>>>(x, w, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+  kern<<<grid, WM * WN * 32, smem, st>>>(x, w, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit, seg);
   B200P_LAUNCH_CHECK("gemm_mma_kernel");
   return B200P_OK;
 }
@@ -269,10 +284,12 @@ constexpr int GK_SLICES = 4, GK_THREADS = 256;
 template <typename T, int MT>     // MT m16 tiles: rows <= 16 * MT
 __global__ void __launch_bounds__(GK_THREADS)
 gemm_stream_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __restrict__ y, int M, int64_t N, int64_t K, int64_t ldx,
-                   int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit) {
+                   int64_t ldw, int64_t ldy, int64_t sx, int64_t sw, int64_t sy, int epi, float limit,
+                   const int32_t* __restrict__ seg) {
   __shared__ float red[GK_SLICES][2][MT][32][4];
   const int64_t z = blockIdx.z;
-  x += z * sx;
+  GEMM_GROUP_ROWS(seg, z, M, x, ldx, sx, ybase, ldy, sy);
+  if (M <= 0) return;                                            // a group nobody was routed to: its weights are not read
   w += z * sw;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nt = warp & 1, ks = warp >> 1;
@@ -323,7 +340,7 @@ gemm_stream_kernel(const T* __restrict__ x, const T* __restrict__ w, void* __res
     for (int hf = 0; hf < 2; ++hf) {
       const int m = i * 16 + (lane >> 2) + hf * 8;
       if (m < M)
-        gemm_store_pair<T>(y, z * sy + (int64_t)m * ldy, (int64_t)blockIdx.x * 16 + nt * 8 + (lane & 3) * 2, N, v[hf * 2], v[hf * 2 + 1],
+        gemm_store_pair<T>(y, ybase + (int64_t)m * ldy, (int64_t)blockIdx.x * 16 + nt * 8 + (lane & 3) * 2, N, v[hf * 2], v[hf * 2 + 1],
                            epi, limit);
     }
   }
@@ -352,9 +369,9 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
     }
     if (M <= 64) {
       dim3 grid((unsigned)((N + 15) / 16), 1, (unsigned)batch);
-      if (M <= 16) gemm_stream_kernel<T, 1><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
-      else if (M <= 32) gemm_stream_kernel<T, 2><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
-      else gemm_stream_kernel<T, 4><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+      if (M <= 16) gemm_stream_kernel<T, 1><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit, nullptr);
+      else if (M <= 32) gemm_stream_kernel<T, 2><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit, nullptr);
+      else gemm_stream_kernel<T, 4><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, (int)M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit, nullptr);
       B200P_LAUNCH_CHECK("gemm_stream_kernel");
       return B200P_OK;
     }
@@ -370,12 +387,61 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
     return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, M, N, K, ldx, ldw, ldy, batch, sx, sw, sy, epi, limit, st);
   }
   dim3 grid((unsigned)((N + GS_BN - 1) / GS_BN), (unsigned)((M + GS_BM - 1) / GS_BM), (unsigned)batch);
-  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit);
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, M, N, K, ldx, ldw, ldy, sx, sw, sy, epi, limit, nullptr);
+  B200P_LAUNCH_CHECK("gemm_simt_kernel");
+  return B200P_OK;
+}
+
+// groups of at most max_rows rows each: the row-streaming kernel while a group fits its 64 rows, 64 x 64 tiles beyond
+template <typename T>
+static int gemm_grouped_dispatch(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+                                 int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t sw, int epi, float limit, bool fast_ok,
+                                 cudaStream_t st) {
+  const T* xp = (const T*)x;
+  const T* wp = (const T*)w;
+  if (fast_ok && max_rows <= 64) {
+    dim3 grid((unsigned)((N + 15) / 16), 1, (unsigned)groups);
+    if (max_rows <= 16) gemm_stream_kernel<T, 1><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, 0, N, K, ldx, ldw, ldy, 0, sw, 0, epi, limit, seg);
+    else if (max_rows <= 32) gemm_stream_kernel<T, 2><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, 0, N, K, ldx, ldw, ldy, 0, sw, 0, epi, limit, seg);
+    else gemm_stream_kernel<T, 4><<<grid, GK_THREADS, 0, st>>>(xp, wp, y, 0, N, K, ldx, ldw, ldy, 0, sw, 0, epi, limit, seg);
+    B200P_LAUNCH_CHECK("gemm_stream_kernel");
+    return B200P_OK;
+  }
+  if (fast_ok) return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, max_rows, N, K, ldx, ldw, ldy, groups, 0, sw, 0, epi, limit, st, seg);
+  dim3 grid((unsigned)((N + GS_BN - 1) / GS_BN), (unsigned)((max_rows + GS_BM - 1) / GS_BM), (unsigned)groups);
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, max_rows, N, K, ldx, ldw, ldy, 0, sw, 0, epi, limit, seg);
   B200P_LAUNCH_CHECK("gemm_simt_kernel");
   return B200P_OK;
 }
 
 }  // namespace b200p
+
+extern "C" int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+                                  int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t stride_w, int dtype, int epilogue,
+                                  float limit, void* stream) {
+  using namespace b200p;
+  B200P_REQUIRE(x && w && y && seg, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && groups > 0 && groups < 65536 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
+  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_SILU, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
+  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
+  B200P_REQUIRE((max_rows + 63) / 64 < 65536, B200P_ERR_ARG, "grid too large");
+  if (max_rows == 0) return B200P_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool fast_ok = dtype != B200P_F32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && stride_w % 8 == 0 && aligned(x, 16) &&
+                       aligned(w, 16);
+  switch (dtype) {
+    case B200P_F32:
+      return gemm_grouped_dispatch<float>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, false, st);
+    case B200P_F16:
+      return gemm_grouped_dispatch<__half>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, fast_ok, st);
+    case B200P_BF16:
+      return gemm_grouped_dispatch<__nv_bfloat16>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit,
+                                                  fast_ok, st);
+    default:
+      set_error("bad dtype %d", dtype);
+      return B200P_ERR_ARG;
+  }
+}
 
 extern "C" int b200p_gemm_set_path(int path) {
   b200p::g_gemm_path = (path == 1 || path == 2) ? path : 0;
@@ -388,8 +454,8 @@ extern "C" int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int6
   using namespace b200p;
   B200P_REQUIRE(x && w && y, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
-  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_CLAMP, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
-  B200P_REQUIRE(epilogue != B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
+  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_SILU, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
+  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
   B200P_REQUIRE((M + 63) / 64 < 65536 && batch < 65536, B200P_ERR_ARG, "grid too large");
   if (M == 0) return B200P_OK;
   cudaStream_t st = (cudaStream_t)stream;

@@ -108,14 +108,10 @@ __device__ __forceinline__ void gemm_tc_store32(const GemmTcParams& p, int64_t r
       for (int i = 0; i < 32; ++i)
         if (n0 + i < p.N) dst[i] = Tr<T>::from_f(v[i]);
     }
-  } else {  // clamped gated unit: columns 2i / 2i+1 are gate_i / up_i
+  } else {  // gated units: columns 2i / 2i+1 are gate_i / up_i
     float a[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float g = fminf(v[2 * i], p.limit);
-      const float u = fminf(fmaxf(v[2 * i + 1], -p.limit), p.limit);
-      a[i] = g / (1.f + __expf(-1.702f * g)) * (u + 1.f);
-    }
+    for (int i = 0; i < 16; ++i) a[i] = glu_unit(v[2 * i], v[2 * i + 1], p.epi, p.limit);
     T* dst = reinterpret_cast<T*>(p.y) + row_off + (n0 >> 1);
     if (p.vec_ok && n0 + 32 <= p.N) {
 #pragma unroll
@@ -139,15 +135,12 @@ __device__ __forceinline__ void gemm_tc_store32(const GemmTcParams& p, int64_t r
 // p.M counts output columns and p.N tokens here.  Gate / up pairs sit in neighbouring lanes.
 template <typename T>
 __device__ __forceinline__ void gemm_tc_store32_trans(const GemmTcParams& p, int64_t z_off, int64_t n, int64_t tok0, const float (&v)[32]) {
-  if (p.epi == B200P_GEMM_GLU_CLAMP) {
+  if (gemm_epi_is_glu(p.epi)) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
-      if (!(threadIdx.x & 1) && n + 1 < p.M && tok0 + i < p.N) {
-        const float g = fminf(v[i], p.limit);
-        const float u = fminf(fmaxf(other, -p.limit), p.limit);
-        reinterpret_cast<T*>(p.y)[z_off + (tok0 + i) * p.ldy + (n >> 1)] = Tr<T>::from_f(g / (1.f + __expf(-1.702f * g)) * (u + 1.f));
-      }
+      if (!(threadIdx.x & 1) && n + 1 < p.M && tok0 + i < p.N)
+        reinterpret_cast<T*>(p.y)[z_off + (tok0 + i) * p.ldy + (n >> 1)] = Tr<T>::from_f(glu_unit(v[i], other, p.epi, p.limit));
     }
     return;
   }

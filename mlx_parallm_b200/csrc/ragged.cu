@@ -112,6 +112,44 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ y, const float* _
   }
 }
 
+// Residual stream of designs whose sublayers are added without a norm of their own (several branches may read one normed
+// input and are summed into the stream together): h += c1 y1 + c2 y2, then the copies the next step needs.
+template <typename T>
+__global__ void residual_add_norm_kernel(float* __restrict__ h, const float* __restrict__ y1, float c1, const float* __restrict__ y2,
+                                         float c2, const float* __restrict__ w_next, T* __restrict__ x_out, T* __restrict__ raw_out,
+                                         int64_t ld_raw, int64_t W, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float* hr = h + row * W;
+  float hs = 0.f;
+  for (int64_t c = threadIdx.x; c < W; c += blockDim.x) {
+    float v = hr[c];
+    if (y1 || y2) {
+      float add = 0.f;
+      if (y1) add = c1 * y1[row * W + c];
+      if (y2) add += c2 * y2[row * W + c];
+      v += add;
+      hr[c] = v;
+    }
+    hs = fmaf(v, v, hs);
+    if (raw_out) raw_out[row * ld_raw + c] = Tr<T>::from_f(v);
+  }
+  if (x_out) {
+    hs = block_sum(hs, red);
+    const float invh = 1.f / sqrtf(hs / (float)W + eps);
+    for (int64_t c = threadIdx.x; c < W; c += blockDim.x) x_out[row * W + c] = Tr<T>::from_f(hr[c] * invh * w_next[c]);
+  }
+}
+
+template <typename T>
+__global__ void cast_columns_kernel(const float* __restrict__ src, int64_t ld_src, T* __restrict__ dst, int64_t ld_dst, int64_t M,
+                                    int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * n) return;
+  const int64_t t = i / n, c = i % n;
+  dst[t * ld_dst + c] = Tr<T>::from_f(src[t * ld_src + c]);
+}
+
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -172,6 +210,30 @@ extern "C" int b200p_norm_add_norm(const float* y, const float* w_post, float* h
   B200P_DISPATCH_DTYPE(dtype, T, (norm_add_norm_kernel<T><<<(unsigned)M, threads, 0, (cudaStream_t)stream>>>(
       y, w_post, h, w_next, (T*)x_out, (T*)raw_out, W, eps)));
   B200P_LAUNCH_CHECK("norm_add_norm_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_residual_add_norm(float* h, const float* y1, float c1, const float* y2, float c2, const float* w_next,
+                                       void* x_out, void* raw_out, int64_t ld_raw, int64_t M, int64_t W, float eps, int dtype,
+                                       void* stream) {
+  B200P_REQUIRE(h && W > 0, B200P_ERR_ARG, "null residual stream");
+  B200P_REQUIRE(!x_out || w_next, B200P_ERR_ARG, "x_out needs its norm weight");
+  B200P_REQUIRE(!raw_out || ld_raw >= W, B200P_ERR_ARG, "raw_out rows are shorter than the stream");
+  if (M == 0) return B200P_OK;
+  const unsigned threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  B200P_DISPATCH_DTYPE(dtype, T, (residual_add_norm_kernel<T><<<(unsigned)M, threads, 0, (cudaStream_t)stream>>>(
+      h, y1, c1, y2, c2, w_next, (T*)x_out, (T*)raw_out, ld_raw, W, eps)));
+  B200P_LAUNCH_CHECK("residual_add_norm_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_cast_columns(const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t M, int64_t n, int dtype,
+                                  void* stream) {
+  B200P_REQUIRE(src && dst && n > 0 && ld_src >= n && ld_dst >= n, B200P_ERR_ARG, "null pointer or bad shape");
+  if (M == 0) return B200P_OK;
+  B200P_DISPATCH_DTYPE(dtype, T, (cast_columns_kernel<T><<<(unsigned)((M * n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      src, ld_src, (T*)dst, ld_dst, M, n)));
+  B200P_LAUNCH_CHECK("cast_columns_kernel");
   return B200P_OK;
 }
 

@@ -5,12 +5,22 @@ layers mix a recurrent state with windowed attention over a shared low-rank late
 
     Linear                  dense [out, in] weight                                 b200p_gemm
     HashedBigramEmbedding   token row * scale + a row picked by (previous, current)  b200p_embed_hashed
-    GatedDeltaMixer         short convolutions + gated delta rule                   b200p_delta_prep / _conv_commit / _scan / _out
+    GatedDeltaMixer         short convolutions + gated delta rule; decay per head   b200p_delta_prep / _conv_commit / _scan / _out
+                            or per key channel, decay and gate optionally low-rank
+    SinkAttention           grouped-head attention, normed q / k, distance bias,    b200p_sink_attn_prep / b200p_sink_attn
+                            query temperature, a sink in the softmax
+    DecayLinearAttention    S <- lambda S + k v^T with constant per-head decays      b200p_linear_attn_prep / b200p_delta_scan / _out
+    SideBySideMixer         several of the above on one input, one fused in- and     b200p_gemm
+                            out-projection, a scale per branch
+    GatedFF                 W_down (act(W_gate x) * W_up x), act in the epilogue     b200p_gemm (fused epilogue)
+    RoutedExperts           top-k routed GatedFF experts + a shared one             b200p_moe_* / b200p_gemm_grouped
     LatentAttention         queries and keys/values through low-rank latents,       b200p_latent_prep / b200p_latent_attn
                             sliding window, optional sharing of another layer's latents
     ClampedGLU              g * sigmoid(1.702 g) * (u + 1) on clamped gate / up      b200p_gemm (fused epilogue)
     TokenSideInput          a small per-layer table indexed by the token, gated      b200p_token_gate
-    SequenceModel           norm -> sublayer -> norm -> residual chain over a ragged batch (b200p_norm_add_norm)
+    SequenceModel           the layer chain over a ragged batch: norm -> sublayer -> norm -> residual (b200p_norm_add_norm), or
+                            one norm feeding a mixer and a feed-forward that are added together, with an optional span of
+                            layers that runs several times on the same weights (b200p_residual_add_norm)
 
 A step is a ragged batch: entry e brings ``counts[e]`` tokens for cache row ``rows[e]``; prompts of different lengths are
 packed back to back (no padding), decode steps bring one token per live row.  Every kernel works from the per-token plan
@@ -26,8 +36,9 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from .._lib import GEMM_GLU_CLAMP, GEMM_STORE, GEMM_STORE_F32
-from .base import DeltaRuleState, LatentKVCache, RowState, TokenState
+from .._lib import (GATE_SIGMOID, GATE_SILU, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_STORE, GEMM_STORE_F32,
+                    SCAN_ACCUMULATE, SCAN_DELTA, SCAN_DELTA_CHANNEL)
+from .base import BatchedKVCache, DeltaRuleState, LatentKVCache, RowState, StateGroup, TokenState
 
 MAX_TOKENS_PER_FORWARD = 8192     # packed tokens of one pass through the layers
 
@@ -50,17 +61,32 @@ class Scratch:
         self.device, self.rows = device, rows
         self._bufs: Dict[tuple, torch.Tensor] = {}
         self._need: Dict[tuple, int] = {}
+        self._flat: Dict[tuple, int] = {}
 
     def reserve(self, name: str, dtype, cols: int):
         key = (name, dtype)
         self._need[key] = max(self._need.get(key, 0), cols)
 
+    def reserve_flat(self, name: str, dtype, n: int):
+        """A buffer of n elements whatever the number of rows (per-step tables such as segment offsets)."""
+        key = (name, dtype)
+        self._flat[key] = max(self._flat.get(key, 0), n)
+
     def allocate(self):
         for key, cols in self._need.items():
             self._bufs[key] = torch.empty((self.rows * cols,), dtype=key[1], device=self.device)
+        for key, n in self._flat.items():
+            self._bufs[key] = torch.zeros((n,), dtype=key[1], device=self.device)
+
+    def flat(self, name: str, dtype) -> torch.Tensor:
+        return self._bufs[(name, dtype)]
 
     def get(self, name: str, dtype, M: int, cols: int) -> torch.Tensor:
         return self._bufs[(name, dtype)][:M * cols].view(M, cols)
+
+
+def _round8(n: int) -> int:
+    return (n + 7) // 8 * 8
 
 
 class GatedDeltaMixer:
@@ -68,21 +94,50 @@ class GatedDeltaMixer:
 
     q, k: ``kv_heads`` heads of ``dim``; v: ``heads`` heads of ``vdim``; head h reads q/k head h // (heads // kv_heads).
     Per head the fp32 state S [dim, vdim] goes S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
-    g = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b).  o is rms-normed over vdim, weighted and gated by
-    silu of a fifth projection before the output projection."""
+    g = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b).  o is rms-normed over vdim, weighted and gated before
+    the output projection.  Options (each a constructor argument):
+      channel_decay  g is a vector over the key channels (one decay per row of S, ``a`` and ``dt_bias`` of heads * dim values)
+                     instead of one number per head;
+      decay_rank     a = W_a2 (W_a1 x) through ``decay_rank`` inner values instead of one projection (0);
+      gate_rank      the gate's pre-activation likewise W_g2 (W_g1 x) (0: one projection);
+      gate_act       "silu" or "sigmoid".
+    Ranks given as None are read from the tensors when the weights are loaded (``set_ranks``)."""
 
-    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, eps: float):
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, eps: float,
+                 channel_decay: bool = False, decay_rank: Optional[int] = 0, gate_rank: Optional[int] = 0, gate_act: str = "silu"):
         self.width, self.heads, self.kv_heads, self.dim, self.vdim, self.taps, self.eps = width, heads, kv_heads, dim, vdim, taps, eps
+        self.channel_decay = channel_decay
+        self.gate_act = {"silu": GATE_SILU, "sigmoid": GATE_SIGMOID}[gate_act]
         self.c_qk = kv_heads * dim
         self.c_v = heads * vdim
+        self.n_decay = heads * (dim if channel_decay else 1)
         self.conv_channels = 2 * self.c_qk + self.c_v
-        self.col_g = self.conv_channels
-        self.col_b = self.col_g + self.c_v
-        self.col_a = self.col_b + heads
-        self.n_proj = self.col_a + heads
-        self.in_proj = Linear(width, self.n_proj)            # rows [q | k | v | gate | b | a]
+        self.col_b = self.conv_channels
+        self.col_g = self.col_b + heads
         self.o_proj = Linear(self.c_v, width)
         self.conv_w = self.A_log = self.dt_bias = self.norm_w = None     # fp32
+        self.decay_rank = self.gate_rank = None
+        self.in_proj = self.decay_up = self.gate_up = None
+        if decay_rank is not None and gate_rank is not None:
+            self.set_ranks(decay_rank, gate_rank)
+
+    def set_ranks(self, decay_rank: int, gate_rank: int):
+        """Lay out the fused input projection: rows [q | k | v | b | gate part | decay part]; a low-rank part holds the inner
+        values (the gate's padded to a multiple of 8 columns so that the decay's start on a 16-byte boundary)."""
+        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.n_g = _round8(gate_rank) if gate_rank else self.c_v
+        self.col_a = self.col_g + self.n_g
+        self.n_proj = self.col_a + (decay_rank if decay_rank else self.n_decay)
+        self.in_proj = Linear(self.width, self.n_proj)
+        self.gate_up = Linear(gate_rank, self.c_v) if gate_rank else None
+        self.decay_up = Linear(decay_rank, self.n_decay) if decay_rank else None
+
+    def stack_in_proj(self, q, k, v, b, gate, decay):
+        """The fused weight from its parts (``gate`` / ``decay``: the first-stage matrices when they are low-rank)."""
+        parts = [q, k, v, b, gate]
+        if self.n_g != gate.shape[0]:
+            parts.append(torch.zeros((self.n_g - gate.shape[0], gate.shape[1]), dtype=gate.dtype))
+        return torch.cat(parts + [decay], 0)
 
     def new_state(self, batch_size: int) -> RowState:
         return DeltaRuleState(self.heads, self.dim, self.vdim, self.conv_channels, self.taps, batch_size)
@@ -93,23 +148,167 @@ class GatedDeltaMixer:
         s.reserve("kn", torch.float32, self.c_qk)
         s.reserve("v", torch.float32, self.c_v)
         s.reserve("beta", torch.float32, self.heads)
-        s.reserve("decay", torch.float32, self.heads)
+        s.reserve("decay", torch.float32, self.n_decay)
         s.reserve("o", torch.float32, self.c_v)
         s.reserve("mix", dt, self.c_v)
+        if self.gate_rank or self.decay_rank:
+            s.reserve("inner", dt, self.n_proj - self.col_g)
+        if self.gate_rank:
+            s.reserve("gate", torch.float32, self.c_v)
+        if self.decay_rank:
+            s.reserve("step", torch.float32, self.n_decay)
 
     def __call__(self, x, y_out, st: DeltaRuleState, plan: dict, s: Scratch, caches):
         M, dt, f32 = x.shape[0], x.dtype, torch.float32
         proj = self.in_proj(x, GEMM_STORE_F32, out=s.get("proj", f32, M, self.n_proj))
+        gate, step = proj[:, self.col_g:self.col_g + self.c_v], proj[:, self.col_a:self.col_a + self.n_decay]
+        if self.gate_rank or self.decay_rank:
+            # second stage of the low-rank parts: the inner values go through the GEMM in the model's storage type
+            inner = proj[:, self.col_g:]
+            if dt != f32:
+                inner = s.get("inner", dt, M, self.n_proj - self.col_g)
+                ops.cast_columns(proj[:, self.col_g:], inner)
+            if self.gate_rank:
+                gate = self.gate_up(inner[:, :self.gate_rank], GEMM_STORE_F32, out=s.get("gate", f32, M, self.c_v))
+            if self.decay_rank:
+                a0 = self.col_a - self.col_g
+                step = self.decay_up(inner[:, a0:a0 + self.decay_rank], GEMM_STORE_F32, out=s.get("step", f32, M, self.n_decay))
         qn, kn = s.get("qn", f32, M, self.c_qk), s.get("kn", f32, M, self.c_qk)
         v, o = s.get("v", f32, M, self.c_v), s.get("o", f32, M, self.c_v)
-        beta, decay = s.get("beta", f32, M, self.heads), s.get("decay", f32, M, self.heads)
-        ops.delta_prep(proj, self.col_b, self.col_a, self.conv_w, st.conv, self.A_log, self.dt_bias, plan["t_row"], plan["t_pos"],
+        beta, decay = s.get("beta", f32, M, self.heads), s.get("decay", f32, M, self.n_decay)
+        ops.delta_prep(proj, self.col_b, step, self.conv_w, st.conv, self.A_log, self.dt_bias, plan["t_row"], plan["t_pos"],
                        plan["t_off"], qn, kn, v, beta, decay, self.heads, self.kv_heads, self.dim, self.vdim, self.taps)
         ops.delta_conv_commit(proj, st.conv, plan["cu"], plan["rows"], plan["nb"], self.conv_channels, self.taps)
         ops.delta_scan(qn, kn, v, beta, decay, st.state, plan["cu"], plan["rows"], plan["lengths"], o, plan["nb"], self.heads,
-                       self.kv_heads, self.dim, self.vdim)
+                       self.kv_heads, self.dim, self.vdim, SCAN_DELTA_CHANNEL if self.channel_decay else SCAN_DELTA)
         mix = s.get("mix", dt, M, self.c_v)
-        ops.delta_out(o, proj, self.col_g, self.norm_w, mix, self.heads, self.vdim, self.eps)
+        ops.delta_out(o, gate, self.norm_w, mix, self.heads, self.vdim, self.eps, self.gate_act)
+        return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
+
+
+class SinkAttention:
+    """A branch of ``SideBySideMixer``: causal attention with ``heads`` query heads over ``kv_heads`` key/value heads (query
+    head h reads h // (heads // kv_heads)), keys of ``dim`` and values of ``vdim``, no rotation.  q and k are rms-normed per
+    head (weights shared by the heads; ``qk_norm`` False: not at all); q at position p is multiplied by
+    1 + temp_coef ln(floor((p + 1) / temp_every) + 1); score = q . k * scale - slope_h (i - j) with
+    slope_h = 2^(slope_log2 (h + 1) / heads) (0: no bias); the softmax denominator also holds exp(sink_h) (``sink`` False:
+    none).  Projection columns [q | k | v]; K and V are cached per position."""
+
+    def __init__(self, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float, qk_norm: bool = True,
+                 temp_coef: float = 0.0, temp_every: float = 1.0, slope_log2: float = 0.0, sink: bool = True):
+        self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.eps = heads, kv_heads, dim, vdim, scale, eps
+        self.qk_norm, self.temp_coef, self.temp_every, self.slope_log2, self.has_sink = qk_norm, temp_coef, temp_every, slope_log2, sink
+        self.col_k = heads * dim
+        self.col_v = self.col_k + kv_heads * dim
+        self.n_proj = self.col_v + kv_heads * vdim
+        self.n_mix = heads * vdim
+        self.q_norm_w = self.k_norm_w = self.sink = None      # fp32
+
+    def new_state(self, batch_size: int) -> RowState:
+        return BatchedKVCache(self.dim, self.kv_heads, batch_size, value_dim=self.vdim)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("aq", torch.float32, self.heads * self.dim)
+
+    def core(self, proj, mix_out, out_scale: float, st: BatchedKVCache, plan: dict, s: Scratch):
+        M = proj.shape[0]
+        q = s.get("aq", torch.float32, M, self.heads * self.dim)
+        ops.sink_attn_prep(proj, 0, self.col_k, self.col_v, self.q_norm_w, self.k_norm_w, self.eps, self.scale, self.temp_coef,
+                           self.temp_every, q, st.keys, st.values, plan["t_row"], plan["t_pos"], self.heads, self.kv_heads, self.dim,
+                           self.vdim)
+        ops.sink_attn(q, st.keys, st.values, plan["t_row"], plan["t_pos"], self.sink, self.slope_log2, mix_out, self.heads,
+                      self.kv_heads, self.dim, self.vdim, out_scale, cu=plan["cu"], rows=plan["rows"], nb=plan["nb"],
+                      max_n=plan["max_n"])
+
+
+class DecayLinearAttention:
+    """A branch of ``SideBySideMixer``: linear attention with a constant decay per head.  q, k (``heads`` x ``dim``) and v
+    (``heads`` x ``vdim``) are silu of their projections; per head the fp32 state S [dim, vdim] goes S <- decay_h S + k v^T,
+    o = S^T q.  All heads are rms-normed as ONE vector (weight of heads * vdim values), gated by sigmoid of a fourth
+    projection.  Projection columns [q | k | v | gate]."""
+
+    def __init__(self, heads: int, dim: int, vdim: int, decay: Sequence[float], eps: float):
+        if len(decay) != heads:
+            raise ValueError("one decay per head")
+        self.heads, self.dim, self.vdim, self.decay_values, self.eps = heads, dim, vdim, [float(d) for d in decay], eps
+        self.c_qk, self.c_v = heads * dim, heads * vdim
+        self.col_g = 2 * self.c_qk + self.c_v
+        self.n_proj = self.col_g + self.c_v
+        self.n_mix = self.c_v
+        self.norm_w = self.decay = None                         # fp32
+
+    def new_state(self, batch_size: int) -> RowState:
+        return DeltaRuleState(self.heads, self.dim, self.vdim, 1, 1, batch_size)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("qn", torch.float32, self.c_qk)
+        s.reserve("kn", torch.float32, self.c_qk)
+        s.reserve("v", torch.float32, self.c_v)
+        s.reserve("decay", torch.float32, self.heads)
+        s.reserve("o", torch.float32, self.c_v)
+
+    def core(self, proj, mix_out, out_scale: float, st: DeltaRuleState, plan: dict, s: Scratch):
+        M, f32 = proj.shape[0], torch.float32
+        qn, kn = s.get("qn", f32, M, self.c_qk), s.get("kn", f32, M, self.c_qk)
+        v, o, decay = s.get("v", f32, M, self.c_v), s.get("o", f32, M, self.c_v), s.get("decay", f32, M, self.heads)
+        ops.linear_attn_prep(proj, self.decay, qn, kn, v, decay, self.heads, self.dim, self.vdim)
+        ops.delta_scan(qn, kn, v, None, decay, st.state, plan["cu"], plan["rows"], plan["lengths"], o, plan["nb"], self.heads,
+                       self.heads, self.dim, self.vdim, SCAN_ACCUMULATE)
+        ops.delta_out(o, proj[:, self.col_g:self.col_g + self.c_v], self.norm_w, mix_out, 1, self.c_v, self.eps, GATE_SIGMOID, out_scale)
+
+
+class SideBySideMixer:
+    """Several mixers that read the same input, y = sum_i scale_i * W_o,i branch_i(x): ONE input projection of all their
+    columns and ONE output projection over their concatenated outputs (each branch scales its output by scale_i before it is
+    rounded to the storage type).  A branch offers n_proj, n_mix, new_state, reserve and
+    core(projection columns, output columns, scale, state, plan, scratch)."""
+
+    def __init__(self, width: int, branches: Sequence, scales: Sequence[float]):
+        self.width, self.branches, self.scales = width, list(branches), [float(c) for c in scales]
+        self.col0, self.mix0 = [], []
+        n = k = 0
+        for b in self.branches:
+            self.col0.append(n)
+            self.mix0.append(k)
+            n += _round8(b.n_proj)             # every branch's columns start on a 32-byte boundary of the fp32 projection
+            k += _round8(b.n_mix)
+        self.n_proj, self.n_mix = n, k
+        self.in_proj = Linear(width, n)
+        self.o_proj = Linear(k, width)
+
+    def stack_in_proj(self, parts: Sequence[torch.Tensor]) -> torch.Tensor:
+        rows = []
+        for b, w in zip(self.branches, parts):
+            rows.append(w)
+            if _round8(b.n_proj) != w.shape[0]:
+                rows.append(torch.zeros((_round8(b.n_proj) - w.shape[0], w.shape[1]), dtype=w.dtype))
+        return torch.cat(rows, 0)
+
+    def stack_o_proj(self, parts: Sequence[torch.Tensor]) -> torch.Tensor:
+        cols = []
+        for b, w in zip(self.branches, parts):
+            cols.append(w)
+            if _round8(b.n_mix) != w.shape[1]:
+                cols.append(torch.zeros((w.shape[0], _round8(b.n_mix) - w.shape[1]), dtype=w.dtype))
+        return torch.cat(cols, 1)
+
+    def new_state(self, batch_size: int) -> RowState:
+        return StateGroup([b.new_state(batch_size) for b in self.branches], batch_size)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("proj", torch.float32, self.n_proj)
+        s.reserve("mix", dt, self.n_mix)
+        for b in self.branches:
+            b.reserve(s, dt)
+
+    def __call__(self, x, y_out, st: StateGroup, plan: dict, s: Scratch, caches):
+        M, dt = x.shape[0], x.dtype
+        proj = self.in_proj(x, GEMM_STORE_F32, out=s.get("proj", torch.float32, M, self.n_proj))
+        mix = s.get("mix", dt, M, self.n_mix)
+        if any(_round8(b.n_mix) != b.n_mix for b in self.branches):
+            mix.zero_()                                        # padding columns meet zero weights, but must not hold NaN
+        for b, c0, m0, scale, part in zip(self.branches, self.col0, self.mix0, self.scales, st.parts):
+            b.core(proj[:, c0:c0 + b.n_proj], mix[:, m0:m0 + b.n_mix], scale, part, plan, s)
         return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
 
 
@@ -165,21 +364,86 @@ class LatentAttention:
         return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
 
 
-class ClampedGLU:
-    """Feed-forward y = W_down (g * sigmoid(1.702 g) * (u + 1)), g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit).
-    gate and up rows are interleaved in one matrix so that the GEMM epilogue holds both values of a hidden unit."""
+class GatedFF:
+    """Feed-forward y = W_down (act(W_gate x) * W_up x) with the gated unit computed in the GEMM epilogue; gate and up rows are
+    interleaved in one matrix so that the epilogue holds both values of a hidden unit.  ``act``: "gelu_tanh", "silu", or
+    "clamped" (g * sigmoid(1.702 g) * (u + 1) on g = min(gate, limit), u = clamp(up, -limit, limit))."""
 
-    def __init__(self, width: int, ff: int, limit: float):
+    EPILOGUES = {"gelu_tanh": GEMM_GLU_GELU_TANH, "silu": GEMM_GLU_SILU, "clamped": GEMM_GLU_CLAMP}
+
+    def __init__(self, width: int, ff: int, act: str, limit: float = 0.0):
         self.width, self.ff, self.limit = width, ff, limit
+        self.epilogue = self.EPILOGUES[act]
         self.gate_up = Linear(width, 2 * ff)
         self.down = Linear(ff, width)
+
+    @staticmethod
+    def interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """rows g0 u0 g1 u1 .. from [ff, width] gate and up."""
+        return torch.stack([gate, up], 1).reshape(2 * gate.shape[0], gate.shape[1])
 
     def reserve(self, s: Scratch, dt):
         s.reserve("act", dt, self.ff)
 
     def __call__(self, x, y_out, s: Scratch):
-        act = self.gate_up(x, GEMM_GLU_CLAMP, out=s.get("act", x.dtype, x.shape[0], self.ff), limit=self.limit)
+        act = self.gate_up(x, self.epilogue, out=s.get("act", x.dtype, x.shape[0], self.ff), limit=self.limit)
         return self.down(act, GEMM_STORE_F32, out=y_out)
+
+
+class ClampedGLU(GatedFF):
+    def __init__(self, width: int, ff: int, limit: float):
+        super().__init__(width, ff, "clamped", limit)
+
+
+class RoutedExperts:
+    """Mixture of ``experts`` GatedFF experts of which every token uses ``top``: router logits W_r x + b in fp32, the ``top``
+    largest chosen, their weights the softmax over the chosen logits alone; y = sum of the chosen experts' weighted outputs,
+    plus a shared expert (``shared_ff`` > 0) that every token uses.  The tokens are sorted by expert on the device and every
+    expert multiplies its own contiguous rows (grouped GEMMs), so the launches do not depend on the routing."""
+
+    def __init__(self, width: int, experts: int, top: int, ff: int, act: str, shared_ff: int = 0, shared_act: Optional[str] = None,
+                 router_bias: bool = True):
+        self.width, self.experts, self.top, self.ff = width, experts, top, ff
+        self.epilogue = GatedFF.EPILOGUES[act]
+        self.router = Linear(width, experts)
+        self.router_bias: Optional[torch.Tensor] = None       # fp32 [experts]
+        self.has_bias = router_bias
+        self.gate_up: Optional[torch.Tensor] = None           # [experts, 2 ff, width], gate / up rows interleaved
+        self.down: Optional[torch.Tensor] = None              # [experts, width, ff]
+        self.shared = GatedFF(width, shared_ff, shared_act or act) if shared_ff else None
+
+    def reserve(self, s: Scratch, dt):
+        f32, i32 = torch.float32, torch.int32
+        s.reserve("router", f32, self.experts)
+        s.reserve("moe_ids", i32, self.top)
+        s.reserve("moe_wts", f32, self.top)
+        s.reserve("moe_slot", i32, self.top)
+        s.reserve("moe_tok", i32, self.top)
+        s.reserve("moe_x", dt, self.top * self.width)
+        s.reserve("moe_act", dt, self.top * self.ff)
+        s.reserve("moe_y", f32, self.top * self.width)
+        s.reserve_flat("moe_seg", i32, self.experts + 1)
+        if self.shared is not None:
+            s.reserve("y_shared", f32, self.width)
+            self.shared.reserve(s, dt)
+
+    def __call__(self, x, y_out, s: Scratch):
+        M, dt, f32, i32 = x.shape[0], x.dtype, torch.float32, torch.int32
+        n = M * self.top
+        logits = self.router(x, GEMM_STORE_F32, out=s.get("router", f32, M, self.experts))
+        ids, wts = s.get("moe_ids", i32, M, self.top), s.get("moe_wts", f32, M, self.top)
+        slot_of, token_of = s.get("moe_slot", i32, M, self.top), s.get("moe_tok", i32, M, self.top)
+        seg = s.flat("moe_seg", i32)
+        ops.moe_route(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top)
+        xs = s.get("moe_x", dt, n, self.width)
+        ops.moe_gather(x, token_of, xs)
+        act = ops.gemm_grouped(xs, self.gate_up, seg, M, self.epilogue, out=s.get("moe_act", dt, n, self.ff))
+        ye = ops.gemm_grouped(act, self.down, seg, M, GEMM_STORE_F32, out=s.get("moe_y", f32, n, self.width))
+        ysh = None
+        if self.shared is not None:
+            ysh = self.shared(x, s.get("y_shared", f32, M, self.width), s)
+        ops.moe_combine(ye, slot_of, wts, ysh, y_out, self.top)
+        return y_out
 
 
 class TokenSideInput:
@@ -222,11 +486,35 @@ class Sublayer:
         self.post_w: Optional[torch.Tensor] = None
 
 
+class LayerRun:
+    """One execution of a layer of the "parallel" chain: x <- x + mixer(n(x)) + mlp(n(x)) with ONE norm n (weight ``norm_w``,
+    fp32, applied as a plain factor).  ``slot`` is the run's entry in the cache list: a layer that runs several times (a looped
+    span) has one run and one state per pass on the same modules.  ``opens``: the run is the first of a pass of the span,
+    which begins with x <- W_in [x ; embedding] (``SequenceModel.loop_in``)."""
+
+    def __init__(self, layer: int, slot: int, mixer, mlp, norm_w_name: str, opens: bool = False):
+        self.layer, self.slot, self.mixer, self.mlp, self.norm_w_name, self.opens = layer, slot, mixer, mlp, norm_w_name, opens
+        self.norm_w: Optional[torch.Tensor] = None
+
+
+def unroll_layers(n_layers: int, start: int = 0, stop: int = 0, times: int = 1) -> List[tuple]:
+    """(layer, opens a pass) in execution order when the layers start .. stop-1 run ``times`` times in a row."""
+    if stop <= start:
+        return [(i, False) for i in range(n_layers)]
+    order = [(i, False) for i in range(start)]
+    for _ in range(times):
+        order += [(i, i == start) for i in range(start, stop)]
+    return order + [(i, False) for i in range(stop, n_layers)]
+
+
 class SequenceModel:
     """callable(inputs [B, L], cache=None, last_only=False, prompt_lengths=None) -> float32 logits, like the other models,
     plus ``forward_ragged`` for prompts of unequal length and arbitrary logit positions.  Subclasses build ``self.embed``,
-    ``self.sublayers`` (in execution order), ``self.mixers`` (one per layer), ``self.final_norm_w`` / ``self.lm_head`` and name
-    their tensors in ``load_weights``."""
+    ``self.final_norm_w`` / ``self.lm_head``, name their tensors in ``load_weights``, and describe their layers in one of two
+    ways: ``block_style`` "sandwich": ``self.sublayers`` (in execution order) and ``self.mixers`` (one per layer), every
+    sublayer between two norms; "parallel": ``self.runs`` (LayerRun, in execution order) and optionally ``self.loop_in``."""
+
+    block_style = "sandwich"
 
     supports_ragged = True
     dense = True                      # unquantised weights: no ``quantization`` block in config.json
@@ -243,6 +531,8 @@ class SequenceModel:
         self.embed: Optional[HashedBigramEmbedding] = None
         self.sublayers: List[Sublayer] = []
         self.mixers: list = []
+        self.runs: List[LayerRun] = []
+        self.loop_in: Optional[Linear] = None         # [width, 2 width]: opens every pass of a looped span
         self.side_table: Optional[torch.Tensor] = None
         self.final_norm_w: Optional[torch.Tensor] = None
         self.lm_head: Optional[Linear] = None
@@ -278,6 +568,8 @@ class SequenceModel:
 
     def new_cache(self, batch_size: int) -> List[RowState]:
         """One entry per layer (its mixer's state) and a last one for the previous token of every row."""
+        if self.block_style == "parallel":
+            return [r.mixer.new_state(batch_size) for r in self.runs] + [TokenState(batch_size)]
         return [m.new_state(batch_size) for m in self.mixers] + [TokenState(batch_size)]
 
     def make_cache(self, batch_size: int, step: Optional[int] = None, paged: bool = True) -> List[RowState]:
@@ -301,6 +593,13 @@ class SequenceModel:
             for sl in self.sublayers:
                 if sl.kind != "mixer":
                     sl.module.reserve(s, dt)
+            for r in self.runs:
+                r.mixer.reserve(s, dt)
+                if r.mlp is not None:
+                    r.mlp.reserve(s, dt)
+                    s.reserve("y2", torch.float32, W)
+            if self.loop_in is not None:
+                s.reserve("cat", dt, 2 * W)
             s.reserve("y", torch.float32, W)
             s.reserve("x", dt, W)
             s.reserve("xl", dt, W)
@@ -336,6 +635,8 @@ class SequenceModel:
         ops.embed_hashed(ids_i32, plan["t_row"], plan["t_pos"], plan["t_off"], cache[-1].last_token, e.weight, e.bigram, h, e.scale,
                          e.buckets, e.mul_prev, e.mul_cur)
         x, y = s.get("x", dt, M, W), s.get("y", torch.float32, M, W)
+        if self.block_style == "parallel":
+            return self._chain_parallel(h, x, y, plan, s, cache, M)
         subs = self.sublayers
 
         def feed(nxt: Optional[Sublayer], y_in, post_w):
@@ -356,6 +657,38 @@ class SequenceModel:
             feed(subs[i + 1] if i + 1 < len(subs) else None, y, sl.post_w)
             if self.residual_tap is not None:
                 self.residual_tap(sl.layer, sl.kind, h)
+
+    def _chain_parallel(self, h, x, y, plan: dict, s: Scratch, cache: List[RowState], M: int):
+        """The runs of a "parallel" model over the residual stream h (fp32): every run reads x = n(h) and adds its branches to h
+        in one pass over the rows, which also prepares what comes next: the next run's normed input, or (before a pass of a
+        looped span) the storage-type copy of h that W_in multiplies beside the embedding."""
+        dt, W, eps, runs = self.dtype, self.args.width, self.eps, self.runs
+        cat = s.get("cat", dt, M, 2 * W) if self.loop_in is not None else None
+
+        def close(i_next: int, y1, y2):
+            nxt = runs[i_next] if i_next < len(runs) else None
+            if nxt is None:
+                if y1 is not None:
+                    ops.residual_add_norm(h, eps, dt, y1=y1, y2=y2)
+            elif nxt.opens:
+                ops.residual_add_norm(h, eps, dt, y1=y1, y2=y2, raw_out=cat[:, :W])
+            else:
+                ops.residual_add_norm(h, eps, dt, y1=y1, y2=y2, w_next=nxt.norm_w, x_out=x)
+            if i_next > 0 and self.residual_tap is not None:
+                self.residual_tap(runs[i_next - 1].layer, "run", h)
+            if nxt is not None and nxt.opens:
+                self.loop_in(cat, GEMM_STORE_F32, out=h)
+                ops.residual_add_norm(h, eps, dt, w_next=nxt.norm_w, x_out=x)
+
+        if cat is not None:
+            ops.residual_add_norm(h, eps, dt, raw_out=cat[:, W:])           # the embedding, for every pass
+        close(0, None, None)
+        for i, r in enumerate(runs):
+            r.mixer(x, y, cache[r.slot], plan, s, cache)
+            y2 = None
+            if r.mlp is not None:
+                y2 = r.mlp(x, s.get("y2", torch.float32, M, W), s)
+            close(i + 1, y, y2)
 
     def _advance_device(self, cache: List[RowState], a: dict, B: int, ids_i32: Optional[torch.Tensor] = None):
         """End of a step on the device: lengths += tokens brought, last token of every entry remembered."""

@@ -113,10 +113,11 @@ class RowState:
 
 
 class BatchedKVCache(RowState):
-    def __init__(self, head_dim, n_kv_heads, batch_size=1):
+    def __init__(self, head_dim, n_kv_heads, batch_size=1, value_dim=None):
         super().__init__(batch_size)
         self.n_kv_heads = n_kv_heads
         self.head_dim = head_dim
+        self.value_dim = head_dim if value_dim is None else value_dim     # designs whose values are not the keys' size
         self.keys: Optional[torch.Tensor] = None
         self.values: Optional[torch.Tensor] = None
 
@@ -160,9 +161,8 @@ class BatchedKVCache(RowState):
             # O(log T) times instead of every ``step`` tokens (the reference concatenates a step-sized block each time,
             # base.py:104-117).  Only ONE layer's old + new buffers are alive at a time.
             new_cap = max(new_cap, ((cap * 3 // 2 + self.step - 1) // self.step) * self.step)
-        shape = (self.batch_size, self.n_kv_heads, new_cap, self.head_dim)
-        nk = torch.zeros(shape, dtype=dtype, device=device)
-        nv = torch.zeros(shape, dtype=dtype, device=device)
+        nk = torch.zeros((self.batch_size, self.n_kv_heads, new_cap, self.head_dim), dtype=dtype, device=device)
+        nv = torch.zeros((self.batch_size, self.n_kv_heads, new_cap, self.value_dim), dtype=dtype, device=device)
         if self.keys is not None and cap > 0:
             keep = min(cap, max(self._offsets) if self._offsets else 0)
             if keep > 0:
@@ -231,6 +231,39 @@ class DeltaRuleState(RowState):
         self.state = torch.zeros((self.batch_size, self.heads, self.key_dim, self.value_dim), dtype=torch.float32, device=device)
         self.conv = torch.zeros((self.batch_size, max(self.taps - 1, 1), self.conv_channels), dtype=torch.float32, device=device)
         return True
+
+
+class StateGroup(RowState):
+    """The states of a layer whose mixer is several mixers side by side (say a KV cache and a matrix state): one entry of the
+    cache list that owns its parts' buffers.  The parts keep no bookkeeping of their own; they follow this entry's rows."""
+
+    def __init__(self, parts: List[RowState], batch_size=1):
+        super().__init__(batch_size)
+        self.parts = list(parts)
+
+    def _follow(self):
+        for p in self.parts:
+            p._offsets = self._offsets
+            p.step = self.step
+
+    def _drop_buffers(self):
+        for p in self.parts:
+            p.batch_size = self.batch_size
+            p._drop_buffers()
+
+    def buffers(self) -> tuple:
+        return tuple(b for p in self.parts for b in p.buffers())
+
+    @property
+    def capacity(self) -> int:
+        return max((p.capacity for p in self.parts), default=0)
+
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        self._follow()
+        moved = False
+        for p in self.parts:
+            moved |= p.ensure_capacity(needed, dtype, device)
+        return moved
 
 
 class TokenState(RowState):

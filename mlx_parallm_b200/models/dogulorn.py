@@ -163,7 +163,7 @@ class Model(SequenceModel):
                 check(q + "q", (m.c_qk, W))
                 check(q + "v", (m.c_v, W))
                 check(q + "q.conv", (m.c_qk, m.taps))
-                m.in_proj.weight = mat(q + "q", q + "k", q + "v", q + "g", q + "b", q + "a")
+                m.in_proj.weight = mat(q + "q", q + "k", q + "v", q + "b", q + "g", q + "a")
                 m.o_proj.weight = mat(q + "o")
                 m.conv_w = vec(q + "q.conv", q + "k.conv", q + "v.conv")
                 m.A_log, m.dt_bias, m.norm_w = vec(q + "A_log"), vec(q + "dt_bias"), vec(q + "norm")

@@ -263,7 +263,7 @@ def gemm(x, w, epilogue=_lib.GEMM_STORE, out=None, limit=0.0, batch=1, strides=(
         assert w.shape[1] == K, (tuple(x.shape), tuple(w.shape))
         ldx, ldw = x.stride(0), w.stride(0)
     if out is None:
-        n_out = N // 2 if epilogue == _lib.GEMM_GLU_CLAMP else N
+        n_out = N // 2 if epilogue >= _lib.GEMM_GLU_CLAMP else N
         out = torch.empty((M, n_out * batch), dtype=torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype, device=x.device)
     if ldy is None:
         ldy = out.stride(0)
@@ -318,12 +318,16 @@ def token_gate(gate, table, ids, out, col0: int):
     return out
 
 
-def delta_prep(proj, col_b, col_a, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps):
-    _dev(proj, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay)
+def delta_prep(proj, col_b, a, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay, H, KH, dk, dv, taps):
+    """``a``: the decay's step input, fp32 [M, H] (one decay per head; may be a column slice of ``proj``) or [M, H * dk] (one
+    per key channel); ``decay`` takes the same shape."""
+    _dev(proj, a, conv_w, conv_state, A_log, dt_bias, t_row, t_pos, t_off, qn, kn, v, beta, decay)
     M = proj.shape[0]
-    _call("b200p_delta_prep", lambda: lib().b200p_delta_prep(_p(proj), proj.stride(0), int(col_b), int(col_a), _p(conv_w), _p(conv_state),
-                                                            _p(A_log), _p(dt_bias), _p(t_row), _p(t_pos), _p(t_off), _p(qn), _p(kn), _p(v),
-                                                            _p(beta), _p(decay), M, H, KH, dk, dv, taps, _stream()))
+    per = a.shape[1] // H
+    assert a.dtype == torch.float32 and a.stride(1) == 1 and a.shape[1] == H * per and decay.shape[1] == H * per and decay.is_contiguous()
+    _call("b200p_delta_prep", lambda: lib().b200p_delta_prep(_p(proj), proj.stride(0), int(col_b), _p(a), a.stride(0), per, _p(conv_w),
+                                                            _p(conv_state), _p(A_log), _p(dt_bias), _p(t_row), _p(t_pos), _p(t_off), _p(qn),
+                                                            _p(kn), _p(v), _p(beta), _p(decay), M, H, KH, dk, dv, taps, _stream()))
 
 
 def delta_conv_commit(proj, conv_state, cu, rows, nb: int, C: int, taps: int):
@@ -332,18 +336,117 @@ def delta_conv_commit(proj, conv_state, cu, rows, nb: int, C: int, taps: int):
                                                                           C, taps, _stream()))
 
 
-def delta_scan(qn, kn, v, beta, decay, state, cu, rows, lengths, o, nb, H, KH, dk, dv):
+def delta_scan(qn, kn, v, beta, decay, state, cu, rows, lengths, o, nb, H, KH, dk, dv, mode=_lib.SCAN_DELTA):
+    """The recurrence over every entry's tokens; ``mode`` one of _lib.SCAN_* (decay per head, per head and key channel, or
+    the plain decayed accumulation without the delta correction)."""
     _dev(qn, kn, v, beta, decay, state, cu, rows, lengths, o)
     assert state.dtype == torch.float32 and state.is_contiguous()
     _call("b200p_delta_scan", lambda: lib().b200p_delta_scan(_p(qn), _p(kn), _p(v), _p(beta), _p(decay), _p(state), _p(cu), _p(rows),
-                                                            _p(lengths), _p(o), nb, H, KH, dk, dv, _stream()))
+                                                            _p(lengths), _p(o), nb, H, KH, dk, dv, int(mode), _stream()))
 
 
-def delta_out(o, proj, col_g, norm_w, out, H, dv, eps):
-    _dev(o, proj, norm_w, out)
+def delta_out(o, gate, norm_w, out, H, dv, eps, gate_act=_lib.GATE_SILU, out_scale=1.0):
+    """out = out_scale * rms_norm(o per group of dv) * norm_w * act(gate); ``gate`` fp32 [M, H * dv] (may be a column slice),
+    ``out`` [M, >= H * dv] (may be a column slice of a wider buffer)."""
+    _dev(o, gate, norm_w, out)
     M = o.shape[0]
-    _call("b200p_delta_out", lambda: lib().b200p_delta_out(_p(o), _p(proj), proj.stride(0), int(col_g), _p(norm_w), _p(out), M, H, dv,
-                                                          float(eps), dtype_code(out.dtype), _stream()))
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.stride(1) == 1 and o.is_contiguous()
+    _call("b200p_delta_out", lambda: lib().b200p_delta_out(_p(o), _p(gate), gate.stride(0), _p(norm_w), _p(out), out.stride(0), M, H, dv,
+                                                          float(eps), int(gate_act), float(out_scale), dtype_code(out.dtype), _stream()))
+
+
+def linear_attn_prep(proj, head_decay, q, k, v, decay, H, dk, dv):
+    """q, k, v = silu of the columns [q | k | v] of ``proj``; decay[t, h] = head_decay[h] (inputs of SCAN_ACCUMULATE)."""
+    _dev(proj, head_decay, q, k, v, decay)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and head_decay.dtype == torch.float32
+    _call("b200p_linear_attn_prep", lambda: lib().b200p_linear_attn_prep(_p(proj), proj.stride(0), _p(head_decay), _p(q), _p(k), _p(v),
+                                                                        _p(decay), M, H, dk, dv, _stream()))
+
+
+def gemm_grouped(x, w, seg, max_rows: int, epilogue=_lib.GEMM_STORE, out=None, limit=0.0):
+    """Rows [seg[z], seg[z+1]) of x times the z-th block of w [groups, N, K] (b200p_gemm_grouped); ``seg`` int32 on the device."""
+    _dev(x, w, seg, out)
+    groups, N, K = w.shape
+    assert x.dtype == w.dtype and x.stride(-1) == 1 and w.is_contiguous() and x.shape[1] == K and seg.dtype == torch.int32
+    glu = epilogue >= _lib.GEMM_GLU_CLAMP
+    want = torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype
+    if out is None:
+        out = torch.empty((x.shape[0], N // 2 if glu else N), dtype=want, device=x.device)
+    assert out.dtype == want and out.stride(-1) == 1
+    _call(("b200p_gemm_grouped", N, K, groups), lambda: lib().b200p_gemm_grouped(
+        _p(x), _p(w), _p(out), _p(seg), int(max_rows), N, K, x.stride(0), K, out.stride(0), groups, N * K, dtype_code(x.dtype), epilogue,
+        float(limit), _stream()))
+    return out
+
+
+def residual_add_norm(h, eps, dtype, y1=None, c1=1.0, y2=None, c2=1.0, w_next=None, x_out=None, raw_out=None):
+    """h += c1 y1 + c2 y2; raw_out = h (may be a column slice); x_out = rms_norm(h) * w_next (b200p_residual_add_norm)."""
+    _dev(h, y1, y2, w_next, x_out, raw_out)
+    M, W = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous()
+    for t in (y1, y2, w_next):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert x_out is None or (x_out.dtype == dtype and x_out.is_contiguous())
+    assert raw_out is None or (raw_out.dtype == dtype and raw_out.stride(1) == 1)
+    _call("b200p_residual_add_norm", lambda: lib().b200p_residual_add_norm(
+        _p(h), _p(y1), float(c1), _p(y2), float(c2), _p(w_next), _p(x_out), _p(raw_out), 0 if raw_out is None else raw_out.stride(0), M, W,
+        float(eps), dtype_code(dtype), _stream()))
+
+
+def cast_columns(src, dst):
+    """dst (16-bit or fp32, may be a column slice) = src (fp32, may be a column slice)."""
+    _dev(src, dst)
+    M, n = src.shape
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape == src.shape
+    _call("b200p_cast_columns", lambda: lib().b200p_cast_columns(_p(src), src.stride(0), _p(dst), dst.stride(0), M, n,
+                                                                dtype_code(dst.dtype), _stream()))
+
+
+def sink_attn_prep(proj, col_q, col_k, col_v, wq, wk, eps, scale, temp_coef, temp_every, q_out, kcache, vcache, t_row, t_pos, H, G, dk, dv):
+    """Queries (normed, scaled, temperature applied) to ``q_out`` fp32; normed keys and the values into the caches
+    [rows, G, Tcap, dk] / [rows, G, Tcap, dv] at every token's (row, position)."""
+    _dev(proj, wq, wk, q_out, kcache, vcache, t_row, t_pos)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype
+    assert kcache.shape[1:] == (G, kcache.shape[2], dk) and vcache.shape[1:] == (G, kcache.shape[2], dv)
+    _call("b200p_sink_attn_prep", lambda: lib().b200p_sink_attn_prep(
+        _p(proj), proj.stride(0), int(col_q), int(col_k), int(col_v), _p(wq), _p(wk), float(eps), float(scale), float(temp_coef),
+        float(temp_every), _p(q_out), _p(kcache), _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), M, H, G, dk, dv,
+        dtype_code(kcache.dtype), _stream()))
+
+
+def sink_attn(q, kcache, vcache, t_row, t_pos, sink, slope_log2, out, H, G, dk, dv, out_scale=1.0, cu=None, rows=None, nb=0, max_n=1):
+    """Causal attention with a distance bias and a sink over the caches; ``out`` [M, >= H * dv] in the caches' dtype."""
+    _dev(q, kcache, vcache, t_row, t_pos, sink, out)
+    M = q.shape[0]
+    assert q.dtype == torch.float32 and q.is_contiguous() and out.stride(1) == 1 and out.dtype == kcache.dtype
+    _call("b200p_sink_attn", lambda: lib().b200p_sink_attn(
+        _p(q), _p(kcache), _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), _p(sink), float(slope_log2), _p(out), out.stride(0),
+        float(out_scale), M, H, G, dk, dv, dtype_code(kcache.dtype), _stream()))
+    return out
+
+
+def moe_route(logits, bias, ids, wts, seg, slot_of, token_of, top: int):
+    _dev(logits, bias, ids, wts, seg, slot_of, token_of)
+    M, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _call("b200p_moe_route", lambda: lib().b200p_moe_route(_p(logits), logits.stride(0), _p(bias), _p(ids), _p(wts), _p(seg), _p(slot_of),
+                                                          _p(token_of), M, E, int(top), _stream()))
+
+
+def moe_gather(x, token_of, xs):
+    _dev(x, token_of, xs)
+    assert x.is_contiguous() and xs.is_contiguous() and x.dtype == xs.dtype and x.shape[1] == xs.shape[1]
+    _call("b200p_moe_gather", lambda: lib().b200p_moe_gather(_p(x), _p(token_of), _p(xs), xs.shape[0], x.shape[1], dtype_code(x.dtype),
+                                                            _stream()))
+
+
+def moe_combine(ye, slot_of, wts, shared_y, y, top: int):
+    _dev(ye, slot_of, wts, shared_y, y)
+    M, W = y.shape
+    assert ye.dtype == torch.float32 and ye.is_contiguous() and y.is_contiguous() and (shared_y is None or shared_y.is_contiguous())
+    _call("b200p_moe_combine", lambda: lib().b200p_moe_combine(_p(ye), _p(slot_of), _p(wts), _p(shared_y), _p(y), M, W, int(top), _stream()))
 
 
 def latent_prep(proj, q_rank, kv_rank, wq, wkv, eps, cq_out, cache, t_row, t_pos):

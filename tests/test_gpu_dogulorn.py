@@ -619,7 +619,7 @@ def test_delta_scan_key_and_value_sizes(dk, dv, H, KH):
     o = torch.empty(M, H * dv, device="cuda")
     p = lambda x: C.c_void_p(x.data_ptr())
     assert L.b200p_delta_scan(p(dev[0]), p(dev[1]), p(dev[2]), p(dev[3]), p(dev[4]), p(dev[5]), p(cu), p(rw), p(ln), p(o), 2, H, KH, dk, dv,
-                              None) == 0
+                              0, None) == 0
     assert (o.double().cpu().view(M, H, dv) - want_o).abs().max() < 1e-4
     assert (dev[5].double().cpu()[[0, 2]] - want_s[[0, 2]]).abs().max() < 1e-4
     assert torch.equal(dev[5].cpu()[1], state0[1])               # a row that no entry names is not touched
