@@ -478,11 +478,12 @@ def _gemm_rooflines(prof, rows, w_bytes_per_el, tflops, hbm_gbs):
 
 def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_decode=32, T_ctx=1024):
     """Prefill and decode throughput of the design at layer sizes of real models (random weights, few layers), beside the
-    Llama graph of this framework at equal width / feed-forward / head count (4-bit weights, its usual format)."""
+    closest existing graph of this framework at equal width / feed-forward / head count: for Dogulorn the Llama graph (4-bit
+    weights, its usual format), for Pupopel the Dogulorn graph (dense bf16 weights, the same ragged engine)."""
     import torch
     from mlx_parallm_b200 import _lib, ops, synth
     from mlx_parallm_b200.utils import DecodeSession, _get_classes
-    assert design == "dogulorn"
+    assert design in ("dogulorn", "pupopel")
     _lib.require_device()
     hbm, src = peaks()
     pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
@@ -493,8 +494,12 @@ def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_
         sz = DESIGN_SIZES[name]
         res = {"size": name, "dims": sz}
         # ---- the design
-        cfg = synth.dogulorn_config(**sz)
-        w = synth.dogulorn_random_weights(cfg, device=dev)
+        if design == "pupopel":
+            cfg = synth.pupopel_config(**sz)
+            w = synth.pupopel_random_weights(cfg, device=dev)
+        else:
+            cfg = synth.dogulorn_config(**sz)
+            w = synth.dogulorn_random_weights(cfg, device=dev)
         Model, Args = _get_classes(cfg)
         model = Model(Args.from_dict(cfg)).load_weights(w, device=dev)
         del w
@@ -534,6 +539,49 @@ def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_
                                                       B_decode, 2, tflops, hbm)
         del model, cache, sess
         torch.cuda.empty_cache()
+        if design == "pupopel":
+            # ---- the closest existing graph at equal size: Dogulorn (dense weights, delta rule + attention, same engine)
+            dcfg = synth.dogulorn_config(**sz)
+            dw = synth.dogulorn_random_weights(dcfg, device=dev)
+            DModel, DArgs = _get_classes(dcfg)
+            dm = DModel(DArgs.from_dict(dcfg)).load_weights(dw, device=dev)
+            del dw
+            torch.cuda.empty_cache()
+
+            def dprefill():
+                return dm.forward_ragged(prompts, dm.make_cache(B_prefill, step=L_prefill + 8))
+            for _ in range(2):
+                dprefill()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                dprefill()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ref = {"prefill": {"batch": B_prefill, "prompt_len": L_prefill, "ms": min(ts), "tok_s": B_prefill * L_prefill / min(ts) * 1e3}}
+            dp = _profile_eager(dprefill, reps=1)
+            ref["prefill_kernels"] = {k: {"calls": v["calls"], "mean_us": round(v["mean_us"], 2)} for k, v in dp.items()}
+            ref["prefill_gemm_roofline"] = _gemm_rooflines(dp, B_prefill * L_prefill, 2, tflops, hbm)
+            dcache = dm.make_cache(B_decode, step=T_ctx + steps + warmup + 64)
+            dm.forward_ragged(ctx, dcache)
+            dsess = DecodeSession(dm, dcache, B_decode, greedy=True)
+            dsess.tok.copy_(torch.randint(0, dcfg["vocab"], (B_decode,), generator=g, device=dev, dtype=torch.int32))
+            dms = time_steps(dsess, steps, warmup)
+            ref["decode"] = {"batch": B_decode, "context": T_ctx, "ms_per_step": dms, "tok_s": B_decode / dms * 1e3}
+            dkp, dl = kernel_profile(dsess, steps=2)
+            ref["decode_kernels"] = {k: {"calls": v["calls_per_step"], "mean_us": round(v["mean_ms"] * 1e3, 2)} for k, v in dkp.items()}
+            ref["decode_launches_per_step"] = dl
+            ref["decode_gemm_roofline"] = _gemm_rooflines({k: {"calls": v["calls_per_step"], "mean_us": v["mean_ms"] * 1e3} for k, v in dkp.items()},
+                                                          B_decode, 2, tflops, hbm)
+            res["dogulorn_equal_size"] = ref
+            res["prefill_kernels"] = {kk: {"calls": v["calls"], "mean_us": round(v["mean_us"], 2)} for kk, v in res["prefill_kernels"].items()}
+            rows_out.append(res)
+            del dm, dcache, dsess
+            torch.cuda.empty_cache()
+            continue
         # ---- the closest existing graph at equal size
         lcfg = dict(model_type="llama", hidden_size=sz["width"], num_hidden_layers=sz["n_layers"], intermediate_size=sz["ff"],
                     num_attention_heads=sz["heads"], num_key_value_heads=max(1, sz["heads"] // 4), rms_norm_eps=1e-5,
@@ -580,9 +628,9 @@ def main():
     ap.add_argument("--sweep", default=",".join(DEFAULT_SWEEP), help="comma list of extra workloads ('' = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["dogulorn"],
+    ap.add_argument("--design", default=None, choices=["dogulorn", "pupopel"],
                     help="instead of the headline workload: prefill / decode throughput of this design at real layer sizes, "
-                         "beside the Llama graph at equal size (one JSON line of its own shape)")
+                         "beside the closest existing graph at equal size (one JSON line of its own shape)")
     ap.add_argument("--design-sizes", default=",".join(DESIGN_SIZES))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

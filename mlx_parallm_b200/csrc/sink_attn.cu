@@ -57,6 +57,7 @@ __global__ void sink_attn_prep_kernel(const float* __restrict__ proj, int64_t ld
   }
 }
 
+constexpr int SINK_ATTN_TILES_MIN_TOKENS = 4;   // shorter portions (and decode steps) take the per-token kernel
 constexpr int SA_KEYS = 32;        // keys per staged chunk: one per lane in the score phase
 constexpr int SA_MAX_HEADS = 8;    // query heads (warps) per CTA
 constexpr int SA_MAX_VL = 16;      // value elements per lane: dv <= 512
@@ -133,6 +134,213 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
   }
 }
 
+// ---- prompts on the tensor cores ------------------------------------------------------------------------------------------
+// CTA = 64 consecutive tokens of one entry x one query head: 4 warps x 16 query rows.  K / V tiles of 64 keys stream
+// global -> shared with cp.async (two stages, XOR-swizzled 16-byte chunks, shared by the four warps); S = Q K^T and O += P V
+// run on mma.sync m16n8k16 with the fp32 online softmax in registers, in base-2 units: the distance bias is added to the
+// scores as -slope log2(e) (p - j), and the running maximum / sum start from the sink (max = sink log2(e), sum = 1).
+constexpr int ST_WARPS = 4, ST_THREADS = ST_WARPS * 32, ST_QT = 16 * ST_WARPS, ST_KT = 64, ST_STAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <typename T, int DK, int DV>
+__global__ void __launch_bounds__(ST_THREADS)
+sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, int64_t Tcap,
+                      const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos,
+                      const float* __restrict__ sink, float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale,
+                      int H, int G) {
+  constexpr int KROW = DK * 2, VROW = DV * 2;                       // bytes per staged row
+  constexpr int K_BYTES = ST_KT * KROW, V_BYTES = ST_KT * VROW, STAGE_BYTES = K_BYTES + V_BYTES;
+  constexpr int KCH = DK / 8, VCH = DV / 8;                         // 16-byte chunks per row
+  extern __shared__ __align__(128) uint8_t st_smem[];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int t_first = cu[e], n_e = cu[e + 1] - t_first;
+  const int q0 = blockIdx.x * ST_QT;
+  if (q0 >= n_e) return;                                            // the same for every thread of the CTA
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad_row = lane >> 2, qc = lane & 3;
+  const int g = h / (H / G);
+  const int p_first = t_pos[t_first];                               // positions of an entry's tokens are consecutive
+  const int l0 = q0 + warp * 16 + quad_row, l1 = l0 + 8;
+  const int lc0 = min(l0, n_e - 1), lc1 = min(l1, n_e - 1);         // rows past the entry compute a valid row, not stored
+  const int pos0 = p_first + lc0, pos1 = p_first + lc1;
+  const int kend = p_first + min(n_e, q0 + ST_QT);                  // keys any row of this CTA may see
+  const int n_tiles = (kend + ST_KT - 1) / ST_KT;
+  const float slope2 = head_slope(slope_log2, h, H) * LOG2E;
+
+  uint32_t qf[DK / 16][4];
+  {
+    const float* p0 = q + ((int64_t)(t_first + lc0) * H + h) * DK;
+    const float* p1 = q + ((int64_t)(t_first + lc1) * H + h) * DK;
+#pragma unroll
+    for (int ks = 0; ks < DK / 16; ++ks) {
+      const float2 a0 = *reinterpret_cast<const float2*>(p0 + ks * 16 + 2 * qc), a1 = *reinterpret_cast<const float2*>(p1 + ks * 16 + 2 * qc);
+      const float2 b0 = *reinterpret_cast<const float2*>(p0 + ks * 16 + 8 + 2 * qc), b1 = *reinterpret_cast<const float2*>(p1 + ks * 16 + 8 + 2 * qc);
+      qf[ks][0] = pack2<T>(a0.x, a0.y);
+      qf[ks][1] = pack2<T>(a1.x, a1.y);
+      qf[ks][2] = pack2<T>(b0.x, b0.y);
+      qf[ks][3] = pack2<T>(b1.x, b1.y);
+    }
+  }
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(st_smem);
+  const int64_t row = rows[e];
+  const T* kbase = kc + (row * G + g) * Tcap * DK;
+  const T* vbase = vc + (row * G + g) * Tcap * DV;
+  auto issue_tile = [&](int tile, int stage) {
+    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
+    const int key0 = tile * ST_KT;
+#pragma unroll
+    for (int i = 0; i < ST_KT * KCH / ST_THREADS; ++i) {
+      const int idx = i * ST_THREADS + threadIdx.x;
+      const int key = idx / KCH, ch = idx % KCH;
+      const bool ok = key0 + key < kend;
+      cp_async16(ks + (uint32_t)(key * KROW + ((ch ^ (key & 7)) << 4)), kbase + (int64_t)(key0 + (ok ? key : 0)) * DK + ch * 8, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < ST_KT * VCH / ST_THREADS; ++i) {
+      const int idx = i * ST_THREADS + threadIdx.x;
+      const int key = idx / VCH, ch = idx % VCH;
+      const bool ok = key0 + key < kend;
+      cp_async16(vs + (uint32_t)(key * VROW + ((ch ^ (key & 7)) << 4)), vbase + (int64_t)(key0 + (ok ? key : 0)) * DV + ch * 8, ok);
+    }
+  };
+
+  float o[DV / 8][4];
+#pragma unroll
+  for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  // the sink opens the softmax: it is the running maximum, and its own term (one) sits in the sum of one thread of the quad
+  const float m_init = sink ? sink[h] * LOG2E : -INFINITY;
+  float m0 = m_init, m1 = m_init;
+  float s0 = (sink && qc == 0) ? 1.f : 0.f, s1 = s0;
+
+  issue_tile(0, 0);
+  cp_async_commit();
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) issue_tile(it + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
+    const int key0 = it * ST_KT;
+    const int mat = lane >> 3, r = lane & 7;
+    float sc[ST_KT / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < ST_KT / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+    for (int np = 0; np < ST_KT / 16; ++np) {
+      const int key = 16 * np + r + 8 * (mat >> 1);
+#pragma unroll
+      for (int kstep = 0; kstep < DK / 16; ++kstep) {
+        const int ch = 2 * kstep + (mat & 1);
+        uint32_t bf[4];
+        ldsm_x4(ks + (uint32_t)(key * KROW + ((ch ^ (key & 7)) << 4)), bf);
+        mma16816<T>(sc[2 * np], qf[kstep], bf[0], bf[1]);
+        mma16816<T>(sc[2 * np + 1], qf[kstep], bf[2], bf[3]);
+      }
+    }
+    float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < ST_KT / 8; ++nt) {
+      const int kcol = key0 + 8 * nt + 2 * qc;
+      sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2 * (float)(pos0 - kcol)) : -INFINITY;
+      sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2 * (float)(pos0 - kcol - 1)) : -INFINITY;
+      sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2 * (float)(pos1 - kcol)) : -INFINITY;
+      sc[nt][3] = kcol + 1 <= pos1 ? fmaf(sc[nt][3], LOG2E, -slope2 * (float)(pos1 - kcol - 1)) : -INFINITY;
+      t0 = fmaxf(t0, fmaxf(sc[nt][0], sc[nt][1]));
+      t1 = fmaxf(t1, fmaxf(sc[nt][2], sc[nt][3]));
+    }
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);      // finite from tile 0 on: key 0 is inside every bound
+    const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < ST_KT / 8; ++nt) {
+      sc[nt][0] = exp2f(sc[nt][0] - mn0); sc[nt][1] = exp2f(sc[nt][1] - mn0);
+      sc[nt][2] = exp2f(sc[nt][2] - mn1); sc[nt][3] = exp2f(sc[nt][3] - mn1);
+      ps0 += sc[nt][0] + sc[nt][1];
+      ps1 += sc[nt][2] + sc[nt][3];
+    }
+    s0 = s0 * corr0 + ps0;
+    s1 = s1 * corr1 + ps1;
+#pragma unroll
+    for (int j = 0; j < DV / 8; ++j) { o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1; }
+#pragma unroll
+    for (int kk = 0; kk < ST_KT / 16; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack2<T>(sc[2 * kk][0], sc[2 * kk][1]);
+      pf[1] = pack2<T>(sc[2 * kk][2], sc[2 * kk][3]);
+      pf[2] = pack2<T>(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      pf[3] = pack2<T>(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+      const int key = 16 * kk + r + 8 * (mat & 1);
+#pragma unroll
+      for (int jp = 0; jp < DV / 16; ++jp) {
+        const int ch = 2 * jp + (mat >> 1);
+        uint32_t bf[4];
+        ldsm_x4_trans(vs + (uint32_t)(key * VROW + ((ch ^ (key & 7)) << 4)), bf);
+        mma16816<T>(o[2 * jp], pf, bf[0], bf[1]);
+        mma16816<T>(o[2 * jp + 1], pf, bf[2], bf[3]);
+      }
+    }
+    __syncthreads();                                 // this stage is refilled by the next iteration's prefetch
+  }
+  cp_async_wait<0>();
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+  const float inv0 = out_scale / s0, inv1 = out_scale / s1;
+  T* o0 = out + (int64_t)(t_first + lc0) * ld_out + (int64_t)h * DV;
+  T* o1 = out + (int64_t)(t_first + lc1) * ld_out + (int64_t)h * DV;
+#pragma unroll
+  for (int j = 0; j < DV / 8; ++j) {
+    const int c = 8 * j + 2 * qc;
+    if (l0 < n_e) *reinterpret_cast<uint32_t*>(o0 + c) = pack2<T>(o[j][0] * inv0, o[j][1] * inv0);
+    if (l1 < n_e) *reinterpret_cast<uint32_t*>(o1 + c) = pack2<T>(o[j][2] * inv1, o[j][3] * inv1);
+  }
+}
+
+template <typename T, int DK, int DV>
+static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
+                                  const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
+                                  float out_scale, int nb, int max_n, int H, int G, cudaStream_t st) {
+  constexpr int smem = ST_STAGES * ST_KT * (DK + DV) * 2;
+  auto kern = sink_attn_tile_kernel<T, DK, DV>;
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(sink_attn_tile_kernel)");
+      attr_set = true;
+    }
+  }
+  dim3 grid((unsigned)((max_n + ST_QT - 1) / ST_QT), (unsigned)H, (unsigned)nb);
+  kern<<<grid, ST_THREADS, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out,
+                                       out_scale, H, G);
+  B200P_LAUNCH_CHECK("sink_attn_tile_kernel");
+  return B200P_OK;
+}
+
+// 1 when the tile kernel takes these sizes (16-bit caches, key and value sizes of 64 or 128)
+static bool sink_attn_tiles_ok(int dk, int dv, int dtype) {
+  return (dtype == B200P_F16 || dtype == B200P_BF16) && (dk == 64 || dk == 128) && (dv == 64 || dv == 128);
+}
+
+template <typename T>
+static int sink_attn_tiles(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
+                           const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
+                           int nb, int max_n, int H, int G, int dk, int dv, cudaStream_t st) {
+#define ST_CASE(DK_, DV_) \
+  if (dk == DK_ && dv == DV_) \
+    return sink_attn_tiles_launch<T, DK_, DV_>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, st)
+  ST_CASE(64, 64);
+  ST_CASE(64, 128);
+  ST_CASE(128, 64);
+  ST_CASE(128, 128);
+#undef ST_CASE
+  set_error("tile attention: unsupported sizes");
+  return B200P_ERR_ARG;
+}
+
 }  // namespace b200p
 
 using namespace b200p;
@@ -171,9 +379,12 @@ static int sink_attn_generic(const float* q, const void* kcache, const void* vca
   return B200P_OK;
 }
 
+extern "C" int b200p_sink_attn_tiles_supported(int dk, int dv, int dtype) { return sink_attn_tiles_ok(dk, dv, dtype) ? 1 : 0; }
+
 extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
-                               const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
-                               float out_scale, int64_t M, int H, int G, int dk, int dv, int dtype, void* stream) {
+                               const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
+                               float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk,
+                               int dv, int dtype, void* stream) {
   B200P_REQUIRE(q && kcache && vcache && t_row && t_pos && out, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(H > 0 && G > 0 && H % G == 0 && G < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dv <= 32 * SA_MAX_VL && dk <= 1024, B200P_ERR_ARG, "value size above %d or key size above 1024 is not built",
@@ -181,6 +392,13 @@ extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* v
   B200P_REQUIRE(ld_out >= (int64_t)H * dv, B200P_ERR_ARG, "output rows are shorter than the heads");
   if (M == 0) return B200P_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  // prompts (entries of several tokens, described by cu / rows) of 16-bit models run on the tensor-core tile kernel
+  if (cu && rows && nb > 0 && max_n >= SINK_ATTN_TILES_MIN_TOKENS && sink_attn_tiles_ok(dk, dv, dtype) && ld_out % 2 == 0 &&
+      aligned(kcache, 16) && aligned(vcache, 16) && aligned(out, 4) && aligned(q, 8) && nb < 65536 && H < 65536) {
+    if (dtype == B200P_F16)
+      return sink_attn_tiles<__half>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv, st);
+    return sink_attn_tiles<__nv_bfloat16>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv, st);
+  }
   switch (dtype) {
     case B200P_F32: return sink_attn_generic<float>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);
     case B200P_F16: return sink_attn_generic<__half>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);

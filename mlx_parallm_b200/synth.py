@@ -291,3 +291,114 @@ def dogulorn_random_weights(cfg: dict, seed: int = 1234, device="cpu") -> Dict[s
             t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
         out[name] = t.to(torch.bfloat16)
     return out
+
+
+# ---- Pupopel ----------------------------------------------------------------------------------------------------------------
+def pupopel_config(width: int, ff: int, n_layers: int, heads: int, head_dim: int, delta_heads: int, delta_kv_heads: int,
+                   delta_dim: int, delta_vdim: int, kv_heads: Optional[int] = None, linear_heads: Optional[int] = None,
+                   experts: int = 16, top: int = 2, vocab: int = 32000, taps: int = 4, loop_times: int = 1, **unused) -> dict:
+    """A config of the design at the sizes of a real model: layers cycle (channel-delta + dense feed-forward, attention beside
+    linear attention + routed experts, the same + dense); the routed layer's active experts and its shared expert together
+    have the dense layer's hidden size.  All layers form one span that runs ``loop_times`` times."""
+    kv_heads = kv_heads or max(1, heads // 4)
+    linear_heads = linear_heads or heads
+    layers = []
+    for i in range(n_layers):
+        kind = i % 3
+        if kind == 0:
+            mixer = {"heads": delta_heads, "kv_heads": delta_kv_heads, "dim": delta_dim, "vdim": delta_vdim, "conv": taps}
+            layers.append({"type": "channel_delta", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+            continue
+        left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                "q_temp": {"coef": 0.1, "every": 512}}
+        right = {"heads": linear_heads, "dim": head_dim, "vdim": head_dim,
+                 "decay": [1.0 - 2.0 ** (-4.0 - 6.0 * h / max(1, linear_heads - 1)) for h in range(linear_heads)]}
+        mixer = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+        if kind == 1:
+            mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // (2 * top)}, "shared": {"ff": ff // 2}}
+        else:
+            mlp = {"kind": "dense", "ff": ff}
+        layers.append({"type": "parallel", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Pupopel", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "loop": {"start": 0, "stop": n_layers, "times": loop_times}}
+
+
+def pupopel_shapes(cfg: dict, rank: Optional[int] = None) -> Dict[str, tuple]:
+    """Shape of every tensor of a Pupopel checkpoint (matrices [out, in]); ``rank``: inner size of the low-rank decay and gate
+    projections (default width / 16, at least 8)."""
+    W, V = cfg["width"], cfg["vocab"]
+    r = rank or max(8, W // 16)
+    out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    loop = cfg.get("loop")
+    if loop and loop["stop"] > loop["start"]:
+        out["loop.in"] = (W, 2 * W)
+
+    def glu(p, ff):
+        out[p + "gate"] = out[p + "up"] = (ff, W)
+        out[p + "down"] = (W, ff)
+
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.mix.", L["mixer"]
+        out[f"l{i}.norm1"] = (W,)
+        if L["type"] == "channel_delta":
+            H, G, dk, dv, n = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"], m.get("conv", 1)
+            for nm, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                out[p + nm] = (rows, W)
+                out[p + nm + ".conv"] = (rows, n)
+            out[p + "b"] = (H, W)
+            out[p + "a1"], out[p + "a2"] = (r, W), (H * dk, r)
+            out[p + "g1"], out[p + "g2"] = (r, W), (H * dv, r)
+            out[p + "A_log"], out[p + "dt_bias"], out[p + "norm"] = (H,), (H * dk,), (dv,)
+            out[p + "o"] = (W, H * dv)
+        else:
+            a, b = m["left"], m["right"]
+            G = a.get("kv_heads", a["heads"])
+            out[p + "left.q"], out[p + "left.k"], out[p + "left.v"] = (a["heads"] * a["dim"], W), (G * a["dim"], W), (G * a["vdim"], W)
+            out[p + "left.q.norm"] = out[p + "left.k.norm"] = (a["dim"],)
+            out[p + "left.sink"] = (a["heads"],)
+            out[p + "left.o"] = (W, a["heads"] * a["vdim"])
+            cq, cv = b["heads"] * b["dim"], b["heads"] * b["vdim"]
+            out[p + "right.q"] = out[p + "right.k"] = (cq, W)
+            out[p + "right.v"] = out[p + "right.g"] = (cv, W)
+            out[p + "right.norm"], out[p + "right.o"] = (cv,), (W, cv)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        q = f"l{i}.mlp."
+        if mlp["kind"] == "dense":
+            glu(q, mlp["ff"])
+        else:
+            for e in range(mlp["router"]["experts"]):
+                glu(f"{q}e{e}.", mlp["expert"]["ff"])
+            out[q + "router"], out[q + "router.b"] = (mlp["router"]["experts"], W), (mlp["router"]["experts"],)
+            if (mlp.get("shared") or {}).get("ff"):
+                glu(q + "shared.", mlp["shared"]["ff"])
+    return out
+
+
+def pupopel_random_weights(cfg: dict, seed: int = 1234, device="cpu", rank: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors: matrices N(0, 1/in), norm offsets N(0, 0.02) (weights that multiply directly: 1 + that), sinks and
+    router biases N(0, 1) / N(0, 0.1), decay parameters spread so that channels forget at different speeds."""
+    dev = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in pupopel_shapes(cfg, rank).items():
+        g = torch.Generator(device=dev)
+        g.manual_seed(_stable_seed(seed, name))
+        if len(shape) == 2 and not name.endswith(".conv"):
+            t = torch.randn(shape, generator=g, device=dev) / math.sqrt(shape[1])
+            if name == "embed":
+                t = t * math.sqrt(shape[1]) * 0.5
+        elif name.endswith(".conv"):
+            t = torch.randn(shape, generator=g, device=dev) * 0.5
+        elif name.endswith("A_log"):
+            t = torch.rand(shape, generator=g, device=dev) * 3.0 - 2.0
+        elif name.endswith("dt_bias") or name.endswith("sink"):
+            t = torch.randn(shape, generator=g, device=dev)
+        elif name.endswith("router.b"):
+            t = 0.1 * torch.randn(shape, generator=g, device=dev)
+        elif name.endswith("norm1") or name == "final.norm":
+            t = 0.02 * torch.randn(shape, generator=g, device=dev)
+        else:
+            t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
+        out[name] = t.to(torch.bfloat16)
+    return out

@@ -211,6 +211,8 @@ def attn_kernel_case(T, H, G, dk, dv, hot_query=None, hot_key=None, sink=None, s
         u = u / u.norm()
         q[hot_query] += boost * u
         k[hot_key] += u.view(1, dk)
+    if dtype != torch.float32:
+        q = q.to(dtype).float()            # the 16-bit kernels round the query to the cache's type: give both sides that query
     sk = torch.zeros(H) if sink is None else sink
     kc = torch.zeros(2, G, T + 3, dk)
     vc = torch.zeros(2, G, T + 3, dv)
@@ -260,7 +262,55 @@ def test_sink_attention_sink_and_bias():
     assert (nob - withb).abs().max() > 1e-2
 
 
-@pytest.mark.parametrize("H,G,dk,dv", [(16, 2, 64, 64), (8, 8, 128, 128), (12, 4, 32, 48), (5, 5, 24, 200), (8, 1, 256, 64)])
+@pytest.mark.parametrize("T,hot_query,hot_key", [(600, 599, 3), (70, 63, 31), (70, 64, 32), (130, 128, 63), (130, 129, 64), (129, 128, 128),
+                                                 (65, 64, 0), (64, 63, 0), (5, 4, 1)])
+def test_sink_attention_tile_kernel_far_keys_and_tile_borders(T, hot_query, hot_key):
+    """Sizes the tensor-core kernel takes (16-bit, key / value sizes 64 and 128): hot pairs across its 64-key tiles and its
+    64-query tiles."""
+    for dk, dv in ((64, 64), (128, 64), (64, 128), (128, 128)):
+        got, want = attn_kernel_case(T, 4, 2, dk, dv, hot_query, hot_key, dtype=torch.bfloat16, sink=torch.tensor([0.5, -1.0, 2.0, 0.0]),
+                                     slope_log2=-8.0 if T < 200 else -20.0, seed=dk + dv)
+        assert (got - want).abs().max() < 3e-2 * max(1.0, float(want.abs().max()))
+        assert float(want[hot_query].abs().max()) > 0.05
+
+
+def test_sink_attention_tiles_over_ragged_portions():
+    """Three entries in one launch: a fresh prompt, a short and a long continuation of rows that already hold keys (their
+    first positions are not multiples of the tile sizes), in rows out of order."""
+    from mlx_parallm_b200 import ops
+    H, G, dk, dv = 6, 3, 64, 128
+    g = torch.Generator().manual_seed(5)
+    entries = [(2, 0, 70), (0, 37, 5), (1, 100, 130)]                    # (cache row, first position, tokens)
+    Tcap = 256
+    kc = (torch.randn(3, G, Tcap, dk, generator=g) * 0.3).to(torch.bfloat16)
+    vc = torch.randn(3, G, Tcap, dv, generator=g).to(torch.bfloat16)
+    M = sum(n for _, _, n in entries)
+    q = (torch.randn(M, H, dk, generator=g) * 0.3).to(torch.bfloat16).float()
+    sink = torch.linspace(-1, 1, H)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    cu, t_row, t_pos = [0], [], []
+    for r, p0, n in entries:
+        cu.append(cu[-1] + n)
+        t_row += [r] * n
+        t_pos += list(range(p0, p0 + n))
+    out = torch.zeros(M, H * dv, dtype=torch.bfloat16, device="cuda")
+    ops.sink_attn(q.reshape(M, -1).contiguous().cuda(), kc.cuda(), vc.cuda(), torch.tensor(t_row, **i32), torch.tensor(t_pos, **i32),
+                  sink.cuda(), -8.0, out, H, G, dk, dv, cu=torch.tensor(cu, **i32), rows=torch.tensor([e[0] for e in entries], **i32),
+                  nb=3, max_n=130)
+    got = out.double().cpu().view(M, H, dv)
+    for t in range(M):
+        r, p = t_row[t], t_pos[t]
+        for h in range(H):
+            kv = h // (H // G)
+            slope = 2.0 ** (-8.0 * (h + 1) / H)
+            s = kc[r, kv, :p + 1].double() @ q[t, h].double() - slope * (p - torch.arange(p + 1)).double()
+            top = max(float(s.max()), float(sink[h]))
+            e = torch.exp(s - top)
+            want = (e @ vc[r, kv, :p + 1].double()) / (e.sum() + math.exp(float(sink[h]) - top))
+            assert (got[t, h] - want).abs().max() < 3e-2 * max(1.0, float(want.abs().max())), (t, h)
+
+
+@pytest.mark.parametrize("H,G,dk,dv", [(16, 2, 64, 64), (8, 8, 128, 128), (12, 4, 32, 48), (5, 5, 24, 200), (8, 1, 256, 64), (4, 2, 64, 128)])
 def test_sink_attention_head_geometries(H, G, dk, dv):
     for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 3e-2)):
         got, want = attn_kernel_case(150, H, G, dk, dv, 149, 20, sink=torch.linspace(-1, 1, H), dtype=dtype, seed=H)
