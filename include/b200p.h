@@ -376,12 +376,16 @@ int b200p_sink_attn_prep(const float* proj, int64_t ldp, int64_t col_q, int64_t 
  * (slope_log2 == 0: no bias); fp32 softmax whose denominator also holds exp(sink[h]) (sink NULL: none);
  * out[t, h, :] (dtype, row stride ld_out) = out_scale * sum_j p_j v_j.  Query head h reads key/value head h / (H / G).
  * With the ragged description (cu, rows, nb entries, the longest of max_n tokens; cu may be NULL) prompts of 16-bit models with
- * key / value sizes of 64 or 128 run on the tensor-core tile kernel; everything else on the per-token kernel. */
+ * key / value sizes of 64 or 128 run on the tensor-core tile kernel, and so do decode steps (max_n == 1, at most 16 query heads
+ * per key/value head) when `workspace` (fp32, 16-byte aligned) holds their partial sums; everything else takes the per-token
+ * kernel. */
 int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
                     const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
                     float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk, int dv,
-                    int dtype, void* stream);
+                    int dtype, void* workspace, size_t workspace_bytes, void* stream);
 int b200p_sink_attn_tiles_supported(int dk, int dv, int dtype);
+/* room for the partial sums of a decode step of nb entries split over the most CTAs the kernel uses (less room: fewer splits) */
+size_t b200p_sink_attn_workspace_bytes(int64_t nb, int H, int dv);
 
 /* Routed experts.  logits fp32 [M, ldl] (+ bias [E] or NULL): ids / wts [M, top] = the `top` largest and the softmax over those;
  * seg [E + 1] = offsets of every expert's rows among the M * top slots; slot_of [M * top] the slot of choice k of token t;

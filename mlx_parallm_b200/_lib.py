@@ -84,7 +84,8 @@ SIGNATURES = {
     "b200p_sink_attn_prep": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _f32, _f32, _f32, _f32, _vp, _vp, _vp, _i64, _vp, _vp,
                                     _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200p_sink_attn": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _f32, _vp, _i64, _f32, _i64, _i32, _i32, _i32,
-                               _i32, _i32, _vp]),
+                               _i32, _i32, _vp, _sz, _vp]),
+    "b200p_sink_attn_workspace_bytes": (_sz, [_i64, _i32, _i32]),
     "b200p_sink_attn_tiles_supported": (_i32, [_i32, _i32, _i32]),
     "b200p_moe_route": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "b200p_moe_gather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),

@@ -3,7 +3,9 @@
 // (score - slope_h (i - j)) and a learned per-head "sink" that joins the softmax denominator without a key or a value.
 //   sink_attn_prep_kernel   norms, temperature and scale on q; normed k and v into the cache at (row, position)     (per token)
 //   sink_attn_kernel        one token x the query heads of one key/value head, fp32 throughout, any sizes           (per token)
-//   sink_attn_tile_kernel   16 query rows per warp on mma.sync, 64-key chunks staged once for the heads of a group   (16-bit caches)
+//   sink_attn_tile_kernel   16 query rows per warp on mma.sync over 64-key tiles: 64 tokens of a prompt for one head, or the
+//                           heads of a key/value head for one decoded token with the keys split over CTAs              (16-bit caches)
+//   sink_attn_merge_kernel  the decode step's partial sums and the sink                                               (per token, head)
 // The softmax starts from the sink: running maximum = sink, running sum = 1 (the sink's own term), accumulator = 0; every key
 // then joins by the usual online update, so a query that sees few keys is damped exactly as the definition says.
 // Every option is a parameter: no norm (weights NULL), no temperature (coef 0), no bias (slope_log2 0), no sink (NULL).
@@ -142,35 +144,51 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
 constexpr int ST_WARPS = 4, ST_THREADS = ST_WARPS * 32, ST_QT = 16 * ST_WARPS, ST_KT = 64, ST_STAGES = 2;
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <typename T, int DK, int DV>
-__global__ void __launch_bounds__(ST_THREADS)
+// DECODE = false: 4 warps, rows = 64 consecutive tokens of entry blockIdx.z for head blockIdx.y (tile blockIdx.x of the entry).
+// DECODE = true: ONE warp per CTA; its 16 rows are the query heads of key/value head blockIdx.y for the single token of entry
+// blockIdx.z, and the CTA takes the blockIdx.x-th share of the key tiles (gridDim.x shares): it writes unnormalised partial
+// sums (o, running max, sum; no sink) that sink_attn_merge_kernel combines.  The keys are then read once for all heads of a
+// group, by many small CTAs at a time.
+template <typename T, int DK, int DV, bool DECODE>
+__global__ void __launch_bounds__(DECODE ? 32 : ST_THREADS)
 sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, int64_t Tcap,
                       const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos,
                       const float* __restrict__ sink, float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale,
-                      int H, int G) {
+                      int H, int G, float* __restrict__ part_o, float* __restrict__ part_ms) {
+  constexpr int NT = DECODE ? 32 : ST_THREADS;
   constexpr int KROW = DK * 2, VROW = DV * 2;                       // bytes per staged row
   constexpr int K_BYTES = ST_KT * KROW, V_BYTES = ST_KT * VROW, STAGE_BYTES = K_BYTES + V_BYTES;
   constexpr int KCH = DK / 8, VCH = DV / 8;                         // 16-byte chunks per row
   extern __shared__ __align__(128) uint8_t st_smem[];
-  const int e = blockIdx.z, h = blockIdx.y;
+  const int e = blockIdx.z;
   const int t_first = cu[e], n_e = cu[e + 1] - t_first;
-  const int q0 = blockIdx.x * ST_QT;
+  const int q0 = DECODE ? 0 : blockIdx.x * ST_QT;
   if (q0 >= n_e) return;                                            // the same for every thread of the CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad_row = lane >> 2, qc = lane & 3;
-  const int g = h / (H / G);
+  const int per = H / G;
+  const int g = DECODE ? blockIdx.y : blockIdx.y / per;
   const int p_first = t_pos[t_first];                               // positions of an entry's tokens are consecutive
-  const int l0 = q0 + warp * 16 + quad_row, l1 = l0 + 8;
-  const int lc0 = min(l0, n_e - 1), lc1 = min(l1, n_e - 1);         // rows past the entry compute a valid row, not stored
-  const int pos0 = p_first + lc0, pos1 = p_first + lc1;
-  const int kend = p_first + min(n_e, q0 + ST_QT);                  // keys any row of this CTA may see
-  const int n_tiles = (kend + ST_KT - 1) / ST_KT;
-  const float slope2 = head_slope(slope_log2, h, H) * LOG2E;
+  const int l0 = q0 + warp * 16 + quad_row, l1 = l0 + 8;            // this thread's two rows: tokens (prompts) or heads (decode)
+  const int n_rows = DECODE ? per : n_e;
+  const int lc0 = min(l0, n_rows - 1), lc1 = min(l1, n_rows - 1);   // rows past the end compute a valid row, not stored
+  const int h0 = DECODE ? g * per + lc0 : blockIdx.y, h1 = DECODE ? g * per + lc1 : blockIdx.y;
+  const int tk0 = DECODE ? t_first : t_first + lc0, tk1 = DECODE ? t_first : t_first + lc1;
+  const int pos0 = DECODE ? p_first : p_first + lc0, pos1 = DECODE ? p_first : p_first + lc1;
+  const int kend = DECODE ? p_first + 1 : p_first + min(n_e, q0 + ST_QT);     // keys any row of this CTA may see
+  const int n_all = (kend + ST_KT - 1) / ST_KT;
+  int tile_lo = 0, tile_hi = n_all;
+  if (DECODE) {
+    const int share = (n_all + gridDim.x - 1) / gridDim.x;
+    tile_lo = blockIdx.x * share;
+    tile_hi = min(n_all, tile_lo + share);
+  }
+  const float slope2_0 = head_slope(slope_log2, h0, H) * LOG2E, slope2_1 = head_slope(slope_log2, h1, H) * LOG2E;
 
   uint32_t qf[DK / 16][4];
   {
-    const float* p0 = q + ((int64_t)(t_first + lc0) * H + h) * DK;
-    const float* p1 = q + ((int64_t)(t_first + lc1) * H + h) * DK;
+    const float* p0 = q + ((int64_t)tk0 * H + h0) * DK;
+    const float* p1 = q + ((int64_t)tk1 * H + h1) * DK;
 #pragma unroll
     for (int ks = 0; ks < DK / 16; ++ks) {
       const float2 a0 = *reinterpret_cast<const float2*>(p0 + ks * 16 + 2 * qc), a1 = *reinterpret_cast<const float2*>(p1 + ks * 16 + 2 * qc);
@@ -189,15 +207,15 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
     const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
     const int key0 = tile * ST_KT;
 #pragma unroll
-    for (int i = 0; i < ST_KT * KCH / ST_THREADS; ++i) {
-      const int idx = i * ST_THREADS + threadIdx.x;
+    for (int i = 0; i < ST_KT * KCH / NT; ++i) {
+      const int idx = i * NT + threadIdx.x;
       const int key = idx / KCH, ch = idx % KCH;
       const bool ok = key0 + key < kend;
       cp_async16(ks + (uint32_t)(key * KROW + ((ch ^ (key & 7)) << 4)), kbase + (int64_t)(key0 + (ok ? key : 0)) * DK + ch * 8, ok);
     }
 #pragma unroll
-    for (int i = 0; i < ST_KT * VCH / ST_THREADS; ++i) {
-      const int idx = i * ST_THREADS + threadIdx.x;
+    for (int i = 0; i < ST_KT * VCH / NT; ++i) {
+      const int idx = i * NT + threadIdx.x;
       const int key = idx / VCH, ch = idx % VCH;
       const bool ok = key0 + key < kend;
       cp_async16(vs + (uint32_t)(key * VROW + ((ch ^ (key & 7)) << 4)), vbase + (int64_t)(key0 + (ok ? key : 0)) * DV + ch * 8, ok);
@@ -208,15 +226,16 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   // the sink opens the softmax: it is the running maximum, and its own term (one) sits in the sum of one thread of the quad
-  const float m_init = sink ? sink[h] * LOG2E : -INFINITY;
-  float m0 = m_init, m1 = m_init;
-  float s0 = (sink && qc == 0) ? 1.f : 0.f, s1 = s0;
+  // (the partial sums of a decode step leave the sink to the merge)
+  const bool open_with_sink = !DECODE && sink;
+  float m0 = open_with_sink ? sink[h0] * LOG2E : -INFINITY, m1 = m0;
+  float s0 = (open_with_sink && qc == 0) ? 1.f : 0.f, s1 = s0;
 
-  issue_tile(0, 0);
+  if (tile_lo < tile_hi) issue_tile(tile_lo, 0);
   cp_async_commit();
-  for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < n_tiles) issue_tile(it + 1, stage ^ 1);
+  for (int it = tile_lo; it < tile_hi; ++it) {
+    const int stage = (it - tile_lo) & 1;
+    if (it + 1 < tile_hi) issue_tile(it + 1, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -242,16 +261,17 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
 #pragma unroll
     for (int nt = 0; nt < ST_KT / 8; ++nt) {
       const int kcol = key0 + 8 * nt + 2 * qc;
-      sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2 * (float)(pos0 - kcol)) : -INFINITY;
-      sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2 * (float)(pos0 - kcol - 1)) : -INFINITY;
-      sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2 * (float)(pos1 - kcol)) : -INFINITY;
-      sc[nt][3] = kcol + 1 <= pos1 ? fmaf(sc[nt][3], LOG2E, -slope2 * (float)(pos1 - kcol - 1)) : -INFINITY;
+      sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2_0 * (float)(pos0 - kcol)) : -INFINITY;
+      sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2_0 * (float)(pos0 - kcol - 1)) : -INFINITY;
+      sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2_1 * (float)(pos1 - kcol)) : -INFINITY;
+      sc[nt][3] = kcol + 1 <= pos1 ? fmaf(sc[nt][3], LOG2E, -slope2_1 * (float)(pos1 - kcol - 1)) : -INFINITY;
       t0 = fmaxf(t0, fmaxf(sc[nt][0], sc[nt][1]));
       t1 = fmaxf(t1, fmaxf(sc[nt][2], sc[nt][3]));
     }
     t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
     t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
-    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);      // finite from tile 0 on: key 0 is inside every bound
+    // finite from a CTA's first tile on: its first key is inside every row's bound (prompts: key 0; decode: one position)
+    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
     const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
     m0 = mn0; m1 = mn1;
     float ps0 = 0.f, ps1 = 0.f;
@@ -288,9 +308,24 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   cp_async_wait<0>();
   s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
   s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+  if constexpr (DECODE) {
+    const int64_t b0 = ((int64_t)e * H + h0) * gridDim.x + blockIdx.x, b1 = ((int64_t)e * H + h1) * gridDim.x + blockIdx.x;
+    if (qc == 0) {
+      if (l0 < per) { part_ms[b0 * 2] = m0; part_ms[b0 * 2 + 1] = s0; }       // a share without tiles leaves (-inf, 0)
+      if (l1 < per) { part_ms[b1 * 2] = m1; part_ms[b1 * 2 + 1] = s1; }
+    }
+    if (tile_lo >= tile_hi) return;
+#pragma unroll
+    for (int j = 0; j < DV / 8; ++j) {
+      const int c = 8 * j + 2 * qc;
+      if (l0 < per) *reinterpret_cast<float2*>(part_o + b0 * DV + c) = make_float2(o[j][0], o[j][1]);
+      if (l1 < per) *reinterpret_cast<float2*>(part_o + b1 * DV + c) = make_float2(o[j][2], o[j][3]);
+    }
+    return;
+  }
   const float inv0 = out_scale / s0, inv1 = out_scale / s1;
-  T* o0 = out + (int64_t)(t_first + lc0) * ld_out + (int64_t)h * DV;
-  T* o1 = out + (int64_t)(t_first + lc1) * ld_out + (int64_t)h * DV;
+  T* o0 = out + (int64_t)tk0 * ld_out + (int64_t)h0 * DV;
+  T* o1 = out + (int64_t)tk1 * ld_out + (int64_t)h1 * DV;
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) {
     const int c = 8 * j + 2 * qc;
@@ -299,12 +334,65 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   }
 }
 
+// out[e's token, h, :] = out_scale * (sum_s o_s 2^(m_s - m)) / (2^(sink log2e - m) + sum_s l_s 2^(m_s - m)), m the largest of them
+template <typename T>
+__global__ void sink_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ms,
+                                       const int32_t* __restrict__ cu, const float* __restrict__ sink, T* __restrict__ out,
+                                       int64_t ld_out, float out_scale, int H, int dv, int splits) {
+  const int e = blockIdx.x, h = blockIdx.y;
+  if (cu[e + 1] - cu[e] <= 0) return;
+  const int64_t base = ((int64_t)e * H + h) * splits;
+  float m = sink ? sink[h] * LOG2E : -INFINITY;
+  for (int sidx = 0; sidx < splits; ++sidx) m = fmaxf(m, part_ms[(base + sidx) * 2]);
+  float den = sink ? exp2f(sink[h] * LOG2E - m) : 0.f;
+  for (int sidx = 0; sidx < splits; ++sidx) {
+    const float ms = part_ms[(base + sidx) * 2];
+    if (ms != -INFINITY) den += part_ms[(base + sidx) * 2 + 1] * exp2f(ms - m);
+  }
+  const float inv = out_scale / den;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float a = 0.f;
+    for (int sidx = 0; sidx < splits; ++sidx) {
+      const float ms = part_ms[(base + sidx) * 2];
+      if (ms != -INFINITY) a = fmaf(part_o[(base + sidx) * dv + c], exp2f(ms - m), a);
+    }
+    out[(int64_t)cu[e] * ld_out + (int64_t)h * dv + c] = Tr<T>::from_f(a * inv);
+  }
+}
+
+constexpr int SINK_ATTN_MAX_SPLITS = 16;
+
 template <typename T, int DK, int DV>
 static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                   const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
-                                  float out_scale, int nb, int max_n, int H, int G, cudaStream_t st) {
+                                  float out_scale, int nb, int max_n, int H, int G, float* ws, size_t ws_bytes, cudaStream_t st) {
   constexpr int smem = ST_STAGES * ST_KT * (DK + DV) * 2;
-  auto kern = sink_attn_tile_kernel<T, DK, DV>;
+  if (max_n == 1) {
+    // decode: shares of the key tiles per (entry, key/value head), as many as keep several CTAs per SM busy and the workspace holds
+    auto kern = sink_attn_tile_kernel<T, DK, DV, true>;
+    static bool attr_set = false;
+    if (smem > 48 * 1024 && !attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(sink_attn_tile_kernel)");
+      attr_set = true;
+    }
+    const size_t per_split = (size_t)nb * H * (DV + 2) * sizeof(float);
+    int splits = (int)((8 * 148 + (int64_t)nb * G - 1) / ((int64_t)nb * G));
+    splits = splits < 1 ? 1 : splits > SINK_ATTN_MAX_SPLITS ? SINK_ATTN_MAX_SPLITS : splits;
+    if ((size_t)splits * per_split > ws_bytes) splits = (int)(ws_bytes / per_split);
+    if (splits < 1) return 1;                                     // no room for partial sums: the caller takes the per-token kernel
+    float* part_o = ws;
+    float* part_ms = ws + (size_t)nb * H * splits * DV;
+    dim3 grid((unsigned)splits, (unsigned)G, (unsigned)nb);
+    kern<<<grid, 32, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out, out_scale,
+                                 H, G, part_o, part_ms);
+    B200P_LAUNCH_CHECK("sink_attn_tile_kernel");
+    sink_attn_merge_kernel<T><<<dim3((unsigned)nb, (unsigned)H), DV >= 128 ? 128 : 64, 0, st>>>(part_o, part_ms, cu, sink, (T*)out, ld_out,
+                                                                                                   out_scale, H, DV, splits);
+    B200P_LAUNCH_CHECK("sink_attn_merge_kernel");
+    return B200P_OK;
+  }
+  auto kern = sink_attn_tile_kernel<T, DK, DV, false>;
   if (smem > 48 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
@@ -315,7 +403,7 @@ static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc
   }
   dim3 grid((unsigned)((max_n + ST_QT - 1) / ST_QT), (unsigned)H, (unsigned)nb);
   kern<<<grid, ST_THREADS, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out,
-                                       out_scale, H, G);
+                                       out_scale, H, G, nullptr, nullptr);
   B200P_LAUNCH_CHECK("sink_attn_tile_kernel");
   return B200P_OK;
 }
@@ -328,10 +416,10 @@ static bool sink_attn_tiles_ok(int dk, int dv, int dtype) {
 template <typename T>
 static int sink_attn_tiles(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                            const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
-                           int nb, int max_n, int H, int G, int dk, int dv, cudaStream_t st) {
+                           int nb, int max_n, int H, int G, int dk, int dv, float* ws, size_t ws_bytes, cudaStream_t st) {
 #define ST_CASE(DK_, DV_) \
   if (dk == DK_ && dv == DV_) \
-    return sink_attn_tiles_launch<T, DK_, DV_>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, st)
+    return sink_attn_tiles_launch<T, DK_, DV_>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, ws, ws_bytes, st)
   ST_CASE(64, 64);
   ST_CASE(64, 128);
   ST_CASE(128, 64);
@@ -381,10 +469,14 @@ static int sink_attn_generic(const float* q, const void* kcache, const void* vca
 
 extern "C" int b200p_sink_attn_tiles_supported(int dk, int dv, int dtype) { return sink_attn_tiles_ok(dk, dv, dtype) ? 1 : 0; }
 
+extern "C" size_t b200p_sink_attn_workspace_bytes(int64_t nb, int H, int dv) {
+  return (size_t)nb * H * SINK_ATTN_MAX_SPLITS * (dv + 2) * sizeof(float);
+}
+
 extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
                                const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
                                float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk,
-                               int dv, int dtype, void* stream) {
+                               int dv, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
   B200P_REQUIRE(q && kcache && vcache && t_row && t_pos && out, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(H > 0 && G > 0 && H % G == 0 && G < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dv <= 32 * SA_MAX_VL && dk <= 1024, B200P_ERR_ARG, "value size above %d or key size above 1024 is not built",
@@ -393,11 +485,17 @@ extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* v
   if (M == 0) return B200P_OK;
   cudaStream_t st = (cudaStream_t)stream;
   // prompts (entries of several tokens, described by cu / rows) of 16-bit models run on the tensor-core tile kernel
-  if (cu && rows && nb > 0 && max_n >= SINK_ATTN_TILES_MIN_TOKENS && sink_attn_tiles_ok(dk, dv, dtype) && ld_out % 2 == 0 &&
+  // and so do decode steps (one token per entry) whose heads per key/value head fit a 16-row tile, given room for partial sums
+  const bool prompts = max_n >= SINK_ATTN_TILES_MIN_TOKENS;
+  const bool decode = max_n == 1 && H / G <= 16 && workspace && aligned(workspace, 16);
+  if (cu && rows && nb > 0 && (prompts || decode) && sink_attn_tiles_ok(dk, dv, dtype) && ld_out % 2 == 0 &&
       aligned(kcache, 16) && aligned(vcache, 16) && aligned(out, 4) && aligned(q, 8) && nb < 65536 && H < 65536) {
-    if (dtype == B200P_F16)
-      return sink_attn_tiles<__half>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv, st);
-    return sink_attn_tiles<__nv_bfloat16>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv, st);
+    const int rc = dtype == B200P_F16
+        ? sink_attn_tiles<__half>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv,
+                                  (float*)workspace, workspace_bytes, st)
+        : sink_attn_tiles<__nv_bfloat16>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G,
+                                         dk, dv, (float*)workspace, workspace_bytes, st);
+    if (rc != 1) return rc;
   }
   switch (dtype) {
     case B200P_F32: return sink_attn_generic<float>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);

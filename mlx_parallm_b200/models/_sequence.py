@@ -207,8 +207,12 @@ class SinkAttention:
     def new_state(self, batch_size: int) -> RowState:
         return BatchedKVCache(self.dim, self.kv_heads, batch_size, value_dim=self.vdim)
 
+    DECODE_WS_ROWS = 256          # decode batches up to this size get the full split of their keys over CTAs, larger ones fewer
+
     def reserve(self, s: Scratch, dt):
         s.reserve("aq", torch.float32, self.heads * self.dim)
+        if dt != torch.float32:
+            s.reserve_flat("attn_ws", torch.float32, ops.sink_attn_workspace_floats(min(s.rows, self.DECODE_WS_ROWS), self.heads, self.vdim))
 
     def core(self, proj, mix_out, out_scale: float, st: BatchedKVCache, plan: dict, s: Scratch):
         M = proj.shape[0]
@@ -218,7 +222,7 @@ class SinkAttention:
                            self.vdim)
         ops.sink_attn(q, st.keys, st.values, plan["t_row"], plan["t_pos"], self.sink, self.slope_log2, mix_out, self.heads,
                       self.kv_heads, self.dim, self.vdim, out_scale, cu=plan["cu"], rows=plan["rows"], nb=plan["nb"],
-                      max_n=plan["max_n"])
+                      max_n=plan["max_n"], workspace=s.flat("attn_ws", torch.float32) if proj.dtype != mix_out.dtype else None)
 
 
 class DecayLinearAttention:

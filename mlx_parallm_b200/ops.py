@@ -416,14 +416,21 @@ def sink_attn_prep(proj, col_q, col_k, col_v, wq, wk, eps, scale, temp_coef, tem
         dtype_code(kcache.dtype), _stream()))
 
 
-def sink_attn(q, kcache, vcache, t_row, t_pos, sink, slope_log2, out, H, G, dk, dv, out_scale=1.0, cu=None, rows=None, nb=0, max_n=1):
-    """Causal attention with a distance bias and a sink over the caches; ``out`` [M, >= H * dv] in the caches' dtype."""
+def sink_attn_workspace_floats(nb: int, H: int, dv: int) -> int:
+    return lib().b200p_sink_attn_workspace_bytes(nb, H, dv) // 4
+
+
+def sink_attn(q, kcache, vcache, t_row, t_pos, sink, slope_log2, out, H, G, dk, dv, out_scale=1.0, cu=None, rows=None, nb=0, max_n=1,
+              workspace=None):
+    """Causal attention with a distance bias and a sink over the caches; ``out`` [M, >= H * dv] in the caches' dtype.
+    ``workspace`` (fp32): room for the partial sums of a decode step on the tile kernel."""
     _dev(q, kcache, vcache, t_row, t_pos, sink, out, cu, rows)
     M = q.shape[0]
     assert q.dtype == torch.float32 and q.is_contiguous() and out.stride(1) == 1 and out.dtype == kcache.dtype
     _call("b200p_sink_attn", lambda: lib().b200p_sink_attn(
         _p(q), _p(kcache), _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), _p(cu), _p(rows), int(nb), int(max_n), _p(sink),
-        float(slope_log2), _p(out), out.stride(0), float(out_scale), M, H, G, dk, dv, dtype_code(kcache.dtype), _stream()))
+        float(slope_log2), _p(out), out.stride(0), float(out_scale), M, H, G, dk, dv, dtype_code(kcache.dtype), _p(workspace),
+        0 if workspace is None else workspace.numel() * 4, _stream()))
     return out
 
 

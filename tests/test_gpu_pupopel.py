@@ -310,6 +310,40 @@ def test_sink_attention_tiles_over_ragged_portions():
             assert (got[t, h] - want).abs().max() < 3e-2 * max(1.0, float(want.abs().max())), (t, h)
 
 
+@pytest.mark.parametrize("H,G,dk,dv,nb", [(8, 2, 64, 64, 5), (16, 1, 128, 128, 3), (4, 4, 64, 128, 40), (6, 3, 128, 64, 300), (32, 2, 64, 64, 2)])
+def test_sink_attention_decode_steps_on_tiles(H, G, dk, dv, nb):
+    """One token per entry at positions from 0 to several hundred (first token, tile borders, many tiles), rows out of order:
+    the keys of an entry are split over several CTAs whose partial sums and the sink are merged afterwards."""
+    from mlx_parallm_b200 import ops
+    g = torch.Generator().manual_seed(H + nb)
+    Tcap = 700
+    special = [0, 1, 63, 64, 65, 127, 128, 129, 699, 640, 300]
+    pos = [special[i] if i < len(special) else int(torch.randint(0, Tcap, (1,), generator=g)) for i in range(nb)]
+    rows = torch.randperm(nb, generator=g).tolist()
+    R = min(nb, 12)                                                        # check these entries against the slow sum
+    kc = (torch.randn(nb, G, Tcap, dk, generator=g) * 0.3).to(torch.bfloat16)
+    vc = torch.randn(nb, G, Tcap, dv, generator=g).to(torch.bfloat16)
+    q = (torch.randn(nb, H, dk, generator=g) * 0.4).to(torch.bfloat16).float()
+    sink = torch.linspace(-2, 2, H)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    out = torch.zeros(nb, H * dv, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(ops.sink_attn_workspace_floats(min(nb, 64), H, dv), device="cuda")
+    ops.sink_attn(q.reshape(nb, -1).contiguous().cuda(), kc.cuda(), vc.cuda(), torch.tensor(rows, **i32), torch.tensor(pos, **i32),
+                  sink.cuda(), -8.0, out, H, G, dk, dv, out_scale=0.8, cu=torch.arange(nb + 1, **i32), rows=torch.tensor(rows, **i32),
+                  nb=nb, max_n=1, workspace=ws)
+    got = out.double().cpu().view(nb, H, dv)
+    for e in range(R):
+        r, p = rows[e], pos[e]
+        for h in range(H):
+            kv = h // (H // G)
+            slope = 2.0 ** (-8.0 * (h + 1) / H)
+            sc = kc[r, kv, :p + 1].double() @ q[e, h].double() - slope * (p - torch.arange(p + 1)).double()
+            top = max(float(sc.max()), float(sink[h]))
+            ex = torch.exp(sc - top)
+            want = 0.8 * (ex @ vc[r, kv, :p + 1].double()) / (ex.sum() + math.exp(float(sink[h]) - top))
+            assert (got[e, h] - want).abs().max() < 2e-2 * max(1.0, float(want.abs().max())), (e, h, p)
+
+
 @pytest.mark.parametrize("H,G,dk,dv", [(16, 2, 64, 64), (8, 8, 128, 128), (12, 4, 32, 48), (5, 5, 24, 200), (8, 1, 256, 64), (4, 2, 64, 128)])
 def test_sink_attention_head_geometries(H, G, dk, dv):
     for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 3e-2)):
