@@ -284,8 +284,9 @@ int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int64_t N, int6
 
 /* Grouped product (the experts of a mixture): group z < groups multiplies the rows [seg[z], seg[z+1]) of x (and writes the same
  * rows of y) by its own weight block w + z * stride_w ([N, K]); seg is a DEVICE array of groups + 1 ascending offsets and
- * max_rows an upper bound of a group's row count, which sizes the launch (so the launch does not depend on the routing). */
-int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+ * max_rows an upper bound of a group's row count, which sizes the launch (so the launch does not depend on the routing);
+ * total_rows = rows of x and y (seg[groups] <= total_rows).  16-bit calls of more than 64 rows per group run on tcgen05. */
+int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t total_rows, int64_t max_rows, int64_t N, int64_t K,
                        int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t stride_w, int dtype, int epilogue,
                        float limit, void* stream);
 

@@ -78,7 +78,7 @@ SIGNATURES = {
     "b200p_delta_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200p_delta_out": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _i32, _f32, _i32, _vp]),
     "b200p_linear_attn_prep": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
-    "b200p_gemm_grouped": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
+    "b200p_gemm_grouped": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _f32, _vp]),
     "b200p_residual_add_norm": (_i32, [_vp, _vp, _f32, _vp, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp]),
     "b200p_cast_columns": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp]),
     "b200p_sink_attn_prep": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _f32, _f32, _f32, _f32, _vp, _vp, _vp, _i64, _vp, _vp,

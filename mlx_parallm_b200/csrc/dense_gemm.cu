@@ -17,6 +17,10 @@ namespace b200p {
 template <typename T>
 int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy,
                    int64_t batch, int64_t sx, int64_t sw, int64_t sy, int epi, float limit, cudaStream_t st);
+template <typename T>
+int gemm_tc_launch_grouped(const T* x, const T* w, void* y, const int32_t* seg, int64_t total_rows, int64_t max_rows, int64_t N,
+                           int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t sw, int epi, float limit,
+                           cudaStream_t st);
 // 0: tcgen05 from 9 rows up (its decode variant streams the weights 1.0-2.3x faster than gemm_stream_kernel at 16 rows, 1.1-2.6x at
 //    32, 1.6-4.4x at 64), the mma.sync kernels where it declines; 1: mma.sync kernels only; 2: the same as 0
 static int g_gemm_path = 0;
@@ -394,7 +398,7 @@ static int gemm_dispatch(const void* x, const void* w, void* y, int64_t M, int64
 
 // groups of at most max_rows rows each: the row-streaming kernel while a group fits its 64 rows, 64 x 64 tiles beyond
 template <typename T>
-static int gemm_grouped_dispatch(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+static int gemm_grouped_dispatch(const void* x, const void* w, void* y, const int32_t* seg, int64_t total_rows, int64_t max_rows, int64_t N, int64_t K,
                                  int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t sw, int epi, float limit, bool fast_ok,
                                  cudaStream_t st) {
   const T* xp = (const T*)x;
@@ -407,7 +411,15 @@ static int gemm_grouped_dispatch(const void* x, const void* w, void* y, const in
     B200P_LAUNCH_CHECK("gemm_stream_kernel");
     return B200P_OK;
   }
-  if (fast_ok) return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, max_rows, N, K, ldx, ldw, ldy, groups, 0, sw, 0, epi, limit, st, seg);
+  if (fast_ok) {
+    if constexpr (!std::is_same<T, float>::value) {
+      if (g_gemm_path != 1) {
+        const int rc = gemm_tc_launch_grouped<T>(xp, wp, y, seg, total_rows, max_rows, N, K, ldx, ldw, ldy, groups, sw, epi, limit, st);
+        if (rc != 1) return rc;
+      }
+    }
+    return gemm_mma_launch<T, 2, 2, 32, 32, 32, 3>(xp, wp, y, max_rows, N, K, ldx, ldw, ldy, groups, 0, sw, 0, epi, limit, st, seg);
+  }
   dim3 grid((unsigned)((N + GS_BN - 1) / GS_BN), (unsigned)((max_rows + GS_BM - 1) / GS_BM), (unsigned)groups);
   gemm_simt_kernel<T><<<grid, 256, 0, st>>>(xp, wp, y, max_rows, N, K, ldx, ldw, ldy, 0, sw, 0, epi, limit, seg);
   B200P_LAUNCH_CHECK("gemm_simt_kernel");
@@ -416,11 +428,12 @@ static int gemm_grouped_dispatch(const void* x, const void* w, void* y, const in
 
 }  // namespace b200p
 
-extern "C" int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t max_rows, int64_t N, int64_t K,
+extern "C" int b200p_gemm_grouped(const void* x, const void* w, void* y, const int32_t* seg, int64_t total_rows, int64_t max_rows, int64_t N, int64_t K,
                                   int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t stride_w, int dtype, int epilogue,
                                   float limit, void* stream) {
   using namespace b200p;
   B200P_REQUIRE(x && w && y && seg, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(total_rows >= max_rows, B200P_ERR_ARG, "x has fewer rows than a group may have");
   B200P_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && groups > 0 && groups < 65536 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
   B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_SILU, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
   B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
@@ -431,11 +444,11 @@ extern "C" int b200p_gemm_grouped(const void* x, const void* w, void* y, const i
                        aligned(w, 16);
   switch (dtype) {
     case B200P_F32:
-      return gemm_grouped_dispatch<float>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, false, st);
+      return gemm_grouped_dispatch<float>(x, w, y, seg, total_rows, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, false, st);
     case B200P_F16:
-      return gemm_grouped_dispatch<__half>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, fast_ok, st);
+      return gemm_grouped_dispatch<__half>(x, w, y, seg, total_rows, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit, fast_ok, st);
     case B200P_BF16:
-      return gemm_grouped_dispatch<__nv_bfloat16>(x, w, y, seg, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit,
+      return gemm_grouped_dispatch<__nv_bfloat16>(x, w, y, seg, total_rows, max_rows, N, K, ldx, ldw, ldy, groups, stride_w, epilogue, limit,
                                                   fast_ok, st);
     default:
       set_error("bad dtype %d", dtype);

@@ -47,7 +47,12 @@ struct GemmTcParams {
   int trans;                     // operands swapped: accumulator row = output column, accumulator column = token
   int epi, vec_ok;
   float limit;
+  // grouped products (not with trans): batch index z owns the rows [seg[z], seg[z+1]) of x and y; tiles past a group's rows are
+  // skipped by every role alike; seg (device, groups + 1 offsets) is copied to shared memory first
+  const int32_t* seg;
+  int groups;
 };
+constexpr int GT_MAX_GROUPS = 1024;
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
   asm volatile(
@@ -168,7 +173,18 @@ struct GemmTcShared {            // lives behind the ring stages (8-byte aligned
   uint64_t full[10], empty[10], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   volatile int abort;
+  int seg[GT_MAX_GROUPS + 1];
 };
+
+// rows of group z that tile mt covers: first row in x / y and how many rows the group has; false when the tile is past them
+__device__ __forceinline__ bool gemm_tc_group_tile(const GemmTcParams& p, const GemmTcShared* sh, int z, int mt, int& first, int& len) {
+  first = 0;
+  len = (int)p.M;
+  if (!p.seg) return true;
+  first = sh->seg[z];
+  len = sh->seg[z + 1] - first;
+  return mt * GT_BM < len;
+}
 
 // bounded wait: gives up after about a second, or as soon as another role of the CTA has given up
 __device__ __forceinline__ bool gemm_tc_wait(uint32_t bar, uint32_t parity, GemmTcShared* sh, int role) {
@@ -223,6 +239,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
     tma_prefetch_desc(&tmw);
   }
   if (warp == 1) tmem_alloc(smem_u32(&sh->tmem_base), TMEM_COLS);
+  if (p.seg)
+    for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) sh->seg[i] = p.seg[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -239,12 +257,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const int z = ts / per_batch, r = ts - z * per_batch;
         const int nt = r / p.tiles_m, mt = r - nt * p.tiles_m;
+        int first, len;
+        if (!gemm_tc_group_tile(p, sh, z, mt, first, len)) continue;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!(ok = gemm_tc_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, sh, 0))) break;
           const uint32_t bar = smem_u32(&sh->full[stage]);
           const uint32_t dst = base + stage * STAGE_BYTES;
           mbar_arrive_expect_tx(bar, STAGE_BYTES);
-          tma_load_3d(dst, &tmx, kb * GT_BK, mt * GT_BM, z, bar);
+          tma_load_3d(dst, &tmx, kb * GT_BK, first + mt * GT_BM, p.seg ? 0 : z, bar);
           tma_load_3d(dst + GT_A_BYTES, &tmw, kb * GT_BK, nt * BN, z, bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -258,6 +278,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        if (p.seg) {
+          const int ts = t / p.splits, z = ts / per_batch, r = ts - z * per_batch;
+          int first, len;
+          if (!gemm_tc_group_tile(p, sh, z, r % p.tiles_m, first, len)) continue;
+        }
         if (!(ok = gemm_tc_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, sh, 1))) break;
         tc_fence_after();
         const uint32_t d = tmem_base + (uint32_t)(acc * BN);
@@ -286,10 +311,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
       const int ts = t / p.splits;
       const int z = ts / per_batch, r = ts - z * per_batch;
       const int nt = r / p.tiles_m, mt = r - nt * p.tiles_m;
+      int first, len;
+      if (!gemm_tc_group_tile(p, sh, z, mt, first, len)) continue;
       if (!gemm_tc_wait(smem_u32(&sh->acc_full[acc]), acc_phase, sh, 2)) break;
       tc_fence_after();
-      const int64_t row = (int64_t)mt * GT_BM + lg * 32 + lane;
-      const int64_t row_off = (int64_t)z * p.sy + row * p.ldy;
+      const int64_t row = (int64_t)mt * GT_BM + lg * 32 + lane;               // within the batch index's (group's) rows
+      const int64_t row_off = p.seg ? (first + row) * p.ldy : (int64_t)z * p.sy + row * p.ldy;
       const uint32_t tsrc = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -300,7 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         tmem_ld16(tsrc + c + 16, *reinterpret_cast<float(*)[16]>(&v[16]));
         tmem_ld_wait();
         if (p.trans) gemm_tc_store32_trans<T>(p, (int64_t)z * p.sy, row, n0, v);
-        else if (row < p.M) gemm_tc_store32<T>(p, row_off, n0, v);
+        else if (row < len) gemm_tc_store32<T>(p, row_off, n0, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -382,6 +409,8 @@ static int gemm_tc_launch_decode(TcEncodeFn enc, const T* x, const T* w, void* y
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;          // no empty split
   p.num_tiles = (int)(tiles * p.splits);
   p.trans = 1;
+  p.seg = nullptr;
+  p.groups = 0;
   p.epi = epi;
   p.limit = limit;
   p.vec_ok = 0;
@@ -423,6 +452,8 @@ int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   p.trans = 0;
+  p.seg = nullptr;
+  p.groups = 0;
   p.epi = epi;
   p.limit = limit;
   const int64_t eb = epi == B200P_GEMM_STORE_F32 ? 4 : 2;
@@ -431,6 +462,49 @@ int gemm_tc_launch(const T* x, const T* w, void* y, int64_t M, int64_t N, int64_
   if (bn == 128) return gemm_tc_run<T, 128, 6>(tmx, tmw, p, st);
   return gemm_tc_run<T, 64, 8>(tmx, tmw, p, st);
 }
+
+// Grouped product: x [total_rows, K] holds the groups' rows back to back (group z: rows [seg[z], seg[z+1]), at most max_rows of
+// them), w [groups][N][K].  The tile list covers max_rows rows for every group; tiles past a group's rows cost a shared-memory
+// read.  A tile's 128-row box may reach into the next group's rows (or past the tensor, which reads zeros): those accumulator
+// rows are not stored.
+template <typename T>
+int gemm_tc_launch_grouped(const T* x, const T* w, void* y, const int32_t* seg, int64_t total_rows, int64_t max_rows, int64_t N,
+                           int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int64_t groups, int64_t sw, int epi, float limit,
+                           cudaStream_t st) {
+  if (K < GT_BK || total_rows >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31) || groups > GT_MAX_GROUPS) return 1;
+  TcEncodeFn enc = gemm_tc_encode_fn();
+  if (!enc) return 1;
+  const int bn = N <= 64 ? 64 : N <= 128 ? 128 : 256;
+  const CUtensorMapDataType dt = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tmx, tmw;
+  if (!gemm_tc_map(enc, &tmx, dt, x, K, total_rows, 1, ldx, 0, GT_BM)) return 1;
+  if (!gemm_tc_map(enc, &tmw, dt, w, K, N, groups, ldw, sw, bn)) return 1;
+  GemmTcParams p;
+  p.y = y;
+  p.M = max_rows; p.N = N; p.K = K; p.ldy = ldy; p.sy = 0;
+  p.tiles_m = (int)((max_rows + GT_BM - 1) / GT_BM);
+  p.tiles_n = (int)((N + bn - 1) / bn);
+  const int64_t nt = (int64_t)p.tiles_m * p.tiles_n * groups;
+  if (nt >= (1ll << 31)) return 1;
+  p.num_tiles = (int)nt;
+  p.num_kb = (int)((K + GT_BK - 1) / GT_BK);
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.trans = 0;
+  p.seg = seg;
+  p.groups = (int)groups;
+  p.epi = epi;
+  p.limit = limit;
+  const int64_t eb = epi == B200P_GEMM_STORE_F32 ? 4 : 2;
+  p.vec_ok = aligned(y, 16) && (ldy * eb) % 16 == 0;
+  if (bn == 256) return gemm_tc_run<T, 256, 4>(tmx, tmw, p, st);
+  if (bn == 128) return gemm_tc_run<T, 128, 6>(tmx, tmw, p, st);
+  return gemm_tc_run<T, 64, 8>(tmx, tmw, p, st);
+}
+template int gemm_tc_launch_grouped<__half>(const __half*, const __half*, void*, const int32_t*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                                            int64_t, int64_t, int64_t, int64_t, int, float, cudaStream_t);
+template int gemm_tc_launch_grouped<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, void*, const int32_t*, int64_t, int64_t,
+                                                   int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, float, cudaStream_t);
 
 template int gemm_tc_launch<__half>(const __half*, const __half*, void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                                     int64_t, int64_t, int64_t, int64_t, int, float, cudaStream_t);

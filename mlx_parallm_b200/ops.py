@@ -375,7 +375,8 @@ def gemm_grouped(x, w, seg, max_rows: int, epilogue=_lib.GEMM_STORE, out=None, l
         out = torch.empty((x.shape[0], N // 2 if glu else N), dtype=want, device=x.device)
     assert out.dtype == want and out.stride(-1) == 1
     _call(("b200p_gemm_grouped", N, K, groups), lambda: lib().b200p_gemm_grouped(
-        _p(x), _p(w), _p(out), _p(seg), int(max_rows), N, K, x.stride(0), K, out.stride(0), groups, N * K, dtype_code(x.dtype), epilogue,
+        _p(x), _p(w), _p(out), _p(seg), x.shape[0], int(max_rows), N, K, x.stride(0), K, out.stride(0), groups, N * K, dtype_code(x.dtype),
+        epilogue,
         float(limit), _stream()))
     return out
 

@@ -129,6 +129,32 @@ def test_routing_and_grouped_products(E, top, M):
         assert (out.cpu().double() - want).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("sizes,N,K", [([130, 0, 77, 300, 1], 264, 128), ([64, 65, 128, 129], 512, 64), ([0, 0, 700], 72, 200), ([90] * 20, 256, 256)])
+def test_grouped_products_of_many_rows(sizes, N, K):
+    """Groups of more than 64 rows (prompts) in 16 bits: groups of 0, 1 and a multiple of the tile's rows, a group that ends
+    where the tensor ends, plain and gated stores."""
+    from mlx_parallm_b200 import _lib, ops
+    from mlx_parallm_b200.models._sequence import GatedFF
+    g = torch.Generator().manual_seed(N + K)
+    E, total = len(sizes), sum(sizes)
+    seg = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device="cuda")
+    x = torch.randn(total, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    y = ops.gemm_grouped(x.cuda(), w.cuda(), seg, max(sizes), _lib.GEMM_STORE_F32).cpu().double()
+    gate, up = w[:, :N // 2], w[:, N // 2:]
+    wi = torch.stack([GatedFF.interleave(gate[e], up[e]) for e in range(E)]).contiguous()
+    act = ops.gemm_grouped(x.cuda(), wi.cuda(), seg, max(sizes), _lib.GEMM_GLU_SILU).cpu().double()
+    lo = 0
+    for e, n in enumerate(sizes):
+        xe = x[lo:lo + n].double()
+        want = xe @ w[e].double().T
+        assert (y[lo:lo + n] - want).abs().max() < 1e-3 if n else True
+        wa = O.silu(xe @ gate[e].double().T) * (xe @ up[e].double().T)
+        assert ((act[lo:lo + n] - wa).abs() / (1.0 + wa.abs())).max() < 2e-2 if n else True
+        lo += n
+    assert _lib.lib().b200p_gemm_tc_fault() == 0
+
+
 def test_residual_add_norm_parts():
     from mlx_parallm_b200 import ops
     g = torch.Generator().manual_seed(1)
