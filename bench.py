@@ -647,7 +647,11 @@ def main():
     cfg_name, B, T = WORKLOADS[args.workload]
 
     if args.design is not None:
-        emit(design_compare(args.design, [x for x in args.design_sizes.split(",") if x], min(args.steps, 64), args.warmup))
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        line = design_compare(args.design, [x for x in args.design_sizes.split(",") if x], min(args.steps, 64), args.warmup)
+        line["clocks"] = sampler.stop()
+        emit(line)
         return
 
     if args.impl == "reference":
