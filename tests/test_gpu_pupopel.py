@@ -407,6 +407,36 @@ def test_bfloat16_model(name):
     assert per_pos[len(t) // 2] < BF16_TOL and per_pos[-1] < 1.0, per_pos[-3:]
 
 
+def test_bfloat16_model_on_the_tensor_core_paths():
+    """Head sizes the tile attention kernels take (64 / 128), groups of experts large enough for the tcgen05 grouped product:
+    a prompt, a ragged batch and decode steps through the captured step (whose attention splits the keys over CTAs) in
+    bfloat16 against the oracle; positions compared by their typical error, as above."""
+    from mlx_parallm_b200 import utils
+    cfg = O.make_config([
+        O.pair_layer(4, 2, 64, 128, 0.125, 2, 64, 64, [0.9, 0.99], q_temp=(0.3, 32), mlp=O.moe_mlp(4, 2, 64, shared_ff=64)),
+        O.delta_layer(2, 2, 64, 64, conv=4, mlp=O.dense_mlp(128)),
+        O.pair_layer(8, 8, 128, 64, 0.09, 1, 32, 32, [0.95]),
+    ], vocab=200, width=128, loop=(0, 2, 2))
+    m, w = build(cfg, seed=7, dtype=torch.bfloat16)
+    t = toks(cfg, 330, 3)
+    want = O.forward(cfg, w, t)
+    got = m.forward_ragged([t[:300]], m.make_cache(1), want=[list(range(300))])
+    per_pos = sorted(O.logits_error(got[i:i + 1], want[i:i + 1]) for i in range(300))
+    assert per_pos[150] < BF16_TOL and per_pos[-1] < 1.0, per_pos[-3:]
+    lens = [300, 70, 5]
+    cache = utils._kv_pool.get_for(m, 3)
+    first = m.forward_ragged([t[:n] for n in lens], cache, rows=[2, 0, 1])
+    errs = [O.logits_error(first[i:i + 1], want[n - 1:n]) for i, n in enumerate(lens)]
+    st = utils._decode_step_for(m, cache, 3, False)
+    st.set_rows([2, 0, 1])
+    for k in range(30):
+        st.tok.copy_(torch.tensor([t[n + k] for n in lens], dtype=torch.int32))
+        st.run()
+        errs += [O.logits_error(st.logits[i:i + 1], want[n + k:n + k + 1]) for i, n in enumerate(lens)]
+    errs.sort()
+    assert errs[len(errs) // 2] < BF16_TOL and errs[-1] < 1.0, errs[-3:]
+
+
 def test_experts_chosen_like_the_oracle(models):
     """The routed layer's choices, read back from the step's scratch, are the oracle's for every token."""
     cfg, m, w = models["mixed"]
