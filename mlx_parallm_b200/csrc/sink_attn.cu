@@ -1,6 +1,7 @@
 // Causal attention over a ragged batch for designs without a positional rotation: grouped query heads, separate key and value
 // sizes, rms-normed queries and keys, a query temperature that depends on the position, a bias linear in the distance
-// (score - slope_h (i - j)) and a learned per-head "sink" that joins the softmax denominator without a key or a value.
+// (score - slope_h (i - j)) and a learned per-head "sink": one extra term exp(sink_h) in the softmax denominator that adds
+// nothing to the output, so it only takes probability mass away from the keys.
 //   sink_attn_prep_kernel   norms, temperature and scale on q; normed k and v into the cache at (row, position)     (per token)
 //   sink_attn_kernel        one token x the query heads of one key/value head, fp32 throughout, any sizes           (per token)
 //   sink_attn_tile_kernel   16 query rows per warp on mma.sync over 64-key tiles: 64 tokens of a prompt for one head, or the

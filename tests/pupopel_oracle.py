@@ -210,7 +210,7 @@ def moe_mlp(experts, top, ff, shared_ff=None):
     return m
 
 
-def make_config(layers, vocab=97, width=48, eps=1e-5, loop=None):
+def make_config(layers, vocab=97, width=48, eps=3e-6, loop=None):
     cfg = {"architecture": "Pupopel", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
     if loop:
         cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
